@@ -1,0 +1,202 @@
+/*
+ * C ABI of the B200 (sm_100a) NVFP4 GEMM / grouped GEMM / fused-MoE library.
+ *
+ * Every entry point takes plain device pointers, integer sizes and a CUDA stream
+ * (cudaStream_t, i.e. an opaque pointer; NULL = the default stream), enqueues work on that
+ * stream and returns at once with an int status (B200_NVFP4_* below). Nothing here
+ * allocates or frees device memory or synchronises, unless a comment says otherwise.
+ * These are the functions a foreign-function binding (ctypes, cgo, JNI, ...) binds; the
+ * C++ API in include/sm120_nvfp4/ is a thin wrapper over them.
+ *
+ * Data formats (same as the reference, include/sm120_nvfp4/gemm.hpp:13-54):
+ *   payload  packed E2M1, two values per byte, low nibble = even k, K contiguous;
+ *   scales   raw UE4M3 bytes, one per 16 consecutive K values, stored in 512-byte atoms
+ *            (128 rows x 4 k-blocks): offset(row, kb) = ((row/128)*ceil(K/64) + kb/4)*512
+ *            + (row%32)*16 + ((row%128)/32)*4 + kb%4; a region holds
+ *            align128(rows) * align4(ceil(K/16)) bytes and must be 16-byte aligned;
+ *   outputs  row-major FP16 (or FP32 where stated).
+ * Shape rules: M, N, K > 0, K % 32 == 0, N % 8 == 0 (src/gemm/cute_gemm.cu:351-355).
+ */
+#ifndef B200_NVFP4_H_
+#define B200_NVFP4_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef B200_NVFP4_API
+#define B200_NVFP4_API __attribute__((visibility("default")))
+#endif
+
+/* Status codes. 0..6 have the values and order of sm120_nvfp4::GemmStatus
+ * (include/sm120_nvfp4/gemm.hpp:56-64). */
+enum {
+  B200_NVFP4_SUCCESS = 0,
+  B200_NVFP4_INVALID_ARGUMENT = 1,
+  B200_NVFP4_UNSUPPORTED_DEVICE = 2,
+  B200_NVFP4_INSUFFICIENT_WORKSPACE = 3,
+  B200_NVFP4_CUTLASS_NOT_SUPPORTED = 4,
+  B200_NVFP4_CUTLASS_ERROR = 5,
+  B200_NVFP4_CUDA_ERROR = 6
+};
+
+/* Paths of the default dispatcher: values of sm120_nvfp4::Nvfp4GemmPath (gemm.hpp:70-74). */
+enum { B200_NVFP4_PATH_GENERIC = 0, B200_NVFP4_PATH_M128_SPLITK4 = 1, B200_NVFP4_PATH_M256_SPLITK2 = 2 };
+
+typedef void* b200_stream_t; /* a cudaStream_t */
+
+/* gemm_status_string (src/gemm/status.cpp:5-23), for every status above. */
+B200_NVFP4_API const char* b200_nvfp4_status_string(int status);
+
+/* nvfp4_gemm_path_string (src/gemm/gemm_dispatch.cu:32-42). */
+B200_NVFP4_API const char* b200_nvfp4_gemm_path_string(int path);
+
+/* nvfp4_gemm_path_sm120 (src/gemm/gemm_dispatch.cu:44-56): deterministic, does not look
+ * at the device. M == 128 -> split-K 4, M == 256 -> split-K 2 when K % 32 == 0,
+ * N % 8 == 0 and ceil(K/128) >= split; otherwise the generic path. */
+B200_NVFP4_API int b200_nvfp4_gemm_path(int m, int n, int k);
+
+/* nvfp4_gemm_workspace_size_sm120 (src/gemm/gemm_dispatch.cu:58-61):
+ * split * M * N * 4 bytes for the two split-K paths, else 0. */
+B200_NVFP4_API size_t b200_nvfp4_gemm_workspace_bytes(int m, int n, int k);
+
+/* nvfp4_cute_gemm_sm120 / nvfp4_cute_gemm_f32_sm120 / nvfp4_cute_batched_gemm(_f32)_sm120
+ * (include/sm120_nvfp4/gemm.hpp:86-113, src/gemm/cute_gemm.cu:357-466).
+ * C[g] = (A[g] * SFA[g]) (B[g] * SFB[g])^T for g < groups; operands contiguous
+ * [groups, M, K/2], [groups, N, K/2], outputs [groups, M, N]; one scale region per group.
+ * out_is_f32 selects FP32 output (the FP32 accumulator, not narrowed). */
+B200_NVFP4_API int b200_nvfp4_gemm(int groups, int m, int n, int k, const void* a, const void* b,
+                                   const void* sfa, const void* sfb, void* c, int out_is_f32,
+                                   b200_stream_t stream);
+
+/* gemm_specialized::m128::launch / m256::launch
+ * (src/gemm/specialized/m128_gemm.cu:417-518): split-K partial sums as FP32
+ * [split_k, M, N] in `workspace`, then C = half(sum over splits, in split order).
+ * Any M is accepted here; the dispatcher only routes M == 128 / 256 to it. */
+B200_NVFP4_API int b200_nvfp4_gemm_splitk(int m, int n, int k, int split_k, const void* a,
+                                          const void* b, const void* sfa, const void* sfb,
+                                          void* c_f16, void* workspace, size_t workspace_bytes,
+                                          b200_stream_t stream);
+
+/* nvfp4_gemm_sm120 (src/gemm/gemm_dispatch.cu:63-90): default dispatcher. */
+B200_NVFP4_API int b200_nvfp4_gemm_auto(int m, int n, int k, const void* a, const void* b,
+                                        const void* sfa, const void* sfb, void* c_f16,
+                                        void* workspace, size_t workspace_bytes,
+                                        b200_stream_t stream);
+
+/* grouped_gemm::group_gemm_nvfp4_async (include/sm120_nvfp4/grouped_gemm.hpp:15-21,
+ * src/grouped_gemm/grouped_gemm.cu:124-144). Rows of group e are
+ * [cu_seqlens[e], cu_seqlens[e] + seqlens[e]) of x [m, K/2]; w is [G, N, K/2]; x_scale has
+ * one region of m_scale_pad * align4(K/16) bytes per group, indexed by the row inside the
+ * group; w_scale one region of align128(N) * align4(K/16) bytes per group. y is FP16
+ * [m, N]; rows that belong to no group are not written. tmas / tiles / cu_tiles are the
+ * reference's per-call scratch: tmas is unused here (may be NULL), tiles [G] and
+ * cu_tiles [G+1] are filled when non-NULL. num_seq_per_group_avg is a scheduling hint only;
+ * update_tma is ignored as in the reference. group_alpha (may be NULL) is an extension with
+ * no counterpart in the reference ABI: one FP32 multiplier per group applied to the FP32
+ * accumulator before the FP16 rounding. G <= 1024. */
+B200_NVFP4_API int b200_nvfp4_grouped_gemm(void* y, const void* x, const void* w,
+                                           const void* seqlens, const void* cu_seqlens,
+                                           const void* x_scale, const void* w_scale, void* tmas,
+                                           void* tiles, void* cu_tiles, int num_group, int m,
+                                           int n, int k, int m_scale_pad,
+                                           int num_seq_per_group_avg, int update_tma,
+                                           const float* group_alpha, b200_stream_t stream);
+
+/* fused_moe::count_and_gather_nvfp4_async (include/sm120_nvfp4/fused_moe.hpp:12-20,
+ * src/fused_moe/count_and_gather.cu:96-143). Slots inside an expert are assigned in
+ * ascending flat assignment index t * num_topk + r (the reference leaves the order to
+ * atomics). zero_scales != 0 reproduces the reference's memset of the whole grouped scale
+ * buffer; 0 skips it (the fused entry points use 0: rows past seqlens[e] are never read
+ * into a stored result). */
+B200_NVFP4_API int b200_nvfp4_moe_count_and_gather(
+    void* gate_up_input, void* gate_up_input_scale, const void* input, const void* input_scale,
+    const void* topk_ids, void* topk_pos, void* seqlens, void* cu_seqlens, int num_tokens,
+    int hidden_size, int num_topk, int num_expert_local, int rank_ep, int input_scale_m_pad,
+    int grouped_scale_m_pad, int zero_scales, b200_stream_t stream);
+
+/* fused_moe::act_mul_and_quant_nvfp4_async (fused_moe.hpp:25-30,
+ * src/fused_moe/activation.cu:170-195): silu(gate) * up -> NVFP4. total_rows bounds the
+ * rows of gate_up and only sizes the grid (0 = unknown); the live row count is read from
+ * cu_seqlens[E] on the device. zero_scales as above. */
+B200_NVFP4_API int b200_nvfp4_moe_act_mul_and_quant(void* output, void* output_scale,
+                                                    const void* gate_up, const void* seqlens,
+                                                    const void* cu_seqlens, int num_expert_local,
+                                                    int total_rows, int grouped_scale_m_pad,
+                                                    int intermediate_size, int zero_scales,
+                                                    b200_stream_t stream);
+
+/* fused_moe::quantize_expert_nvfp4_async (fused_moe.hpp:35-39,
+ * src/fused_moe/activation.cu:197-232): FP16 / BF16 rows -> NVFP4, expert-major. */
+B200_NVFP4_API int b200_nvfp4_moe_quantize_expert(void* output, void* output_scale,
+                                                  const void* input, const void* seqlens,
+                                                  const void* cu_seqlens, int num_expert_local,
+                                                  int total_rows, int hidden_size,
+                                                  int grouped_scale_m_pad, int input_is_bf16,
+                                                  int zero_scales, b200_stream_t stream);
+
+/* fused_moe::reduce_nvfp4_async (fused_moe.hpp:41-45, src/fused_moe/reduce.cu:39-55):
+ * out[t] = half(shared[t] + sum_r w[t,r] * down[pos[t,r]]) in FP32, route order, skipping
+ * pos < 0. out_is_bf16 != 0 (extension) rounds the same FP32 sum to BF16 instead. */
+B200_NVFP4_API int b200_nvfp4_moe_reduce(void* output, const void* down_output,
+                                         const void* topk_pos, const void* topk_scale,
+                                         const void* shared_output, int num_tokens,
+                                         int hidden_size, int num_topk, int out_is_bf16,
+                                         b200_stream_t stream);
+
+/* fused_moe::fuse_moe_nvfp4_async (fused_moe.hpp:49-63, src/fused_moe/fused_moe.cu:25-74).
+ * Same argument list and meaning; every intermediate is caller memory. */
+B200_NVFP4_API int b200_nvfp4_fused_moe(
+    void* output, const void* input, const void* input_scale, void* gate_up_input,
+    void* gate_up_input_scale, void* gate_up_output, const void* gate_up_weight,
+    const void* gate_up_weight_scale, void* gate_up_tmas, void* down_input,
+    void* down_input_scale, void* down_output, const void* down_weight,
+    const void* down_weight_scale, void* down_tmas, const void* topk_ids, const void* topk_scale,
+    void* topk_pos, void* seqlens, void* cu_seqlens, void* tiles, void* cu_tiles,
+    const void* shared_output, int num_tokens, int hidden_size, int intermediate_size,
+    int num_topk, int num_expert_total, int num_expert_local, int rank_ep,
+    int input_scale_m_pad, int grouped_scale_m_pad, b200_stream_t stream);
+
+/* fused_moe::expert_moe_nvfp4_workspace_size (fused_moe.hpp:69-71,
+ * src/fused_moe/fused_moe.cu:76-95): same carve order and 256-byte alignment. */
+B200_NVFP4_API size_t b200_nvfp4_expert_moe_workspace_bytes(int total_rows, int hidden_size,
+                                                            int intermediate_size,
+                                                            int num_expert_local,
+                                                            int grouped_scale_m_pad);
+
+/* fused_moe::expert_moe_nvfp4_async (fused_moe.hpp:73-80, src/fused_moe/fused_moe.cu:97-157).
+ * Returns B200_NVFP4_INSUFFICIENT_WORKSPACE where the reference throws
+ * std::invalid_argument. */
+B200_NVFP4_API int b200_nvfp4_expert_moe(void* output, const void* input, const void* input_scale,
+                                         const void* gate_up_weight,
+                                         const void* gate_up_weight_scale,
+                                         const void* down_weight, const void* down_weight_scale,
+                                         const void* seqlens, const void* cu_seqlens,
+                                         void* workspace, size_t workspace_bytes, int total_rows,
+                                         int hidden_size, int intermediate_size,
+                                         int num_expert_local, int grouped_scale_m_pad,
+                                         b200_stream_t stream);
+
+/* Reads and clears the device word in which a kernel records a timed-out wait (every wait
+ * inside the kernels is bounded). SYNCHRONISES the device. *code receives 0 when nothing
+ * was recorded. No counterpart in the reference. */
+B200_NVFP4_API int b200_nvfp4_device_error(int* code);
+
+/* Forces the tile width (output columns per CTA tile: 32, 64, 128 or 256) of every GEMM
+ * launched afterwards by this process; 0 restores the built-in choice. For tests and
+ * tuning. No counterpart in the reference. Returns B200_NVFP4_INVALID_ARGUMENT for any other
+ * value. */
+B200_NVFP4_API int b200_nvfp4_set_tile_n(int tile_n);
+
+/* Number of kernel launches this library has issued from the calling process since load
+ * (for launch accounting in benchmarks). No counterpart in the reference. */
+B200_NVFP4_API long long b200_nvfp4_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B200_NVFP4_H_ */

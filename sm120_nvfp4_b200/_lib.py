@@ -1,0 +1,83 @@
+"""ctypes binding of the C ABI in include/b200_nvfp4.h.
+
+There is no fallback: if the shared library is missing and cannot be built, importing the
+ops raises. The library is built in-tree by sm120_nvfp4_b200.build.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+_LIB_PATH = _PKG / "libb200_nvfp4.so"
+_lib = None
+
+STATUS_SUCCESS = 0
+STATUS_INVALID_ARGUMENT = 1
+STATUS_UNSUPPORTED_DEVICE = 2
+STATUS_INSUFFICIENT_WORKSPACE = 3
+STATUS_CUDA_ERROR = 6
+
+vp = C.c_void_p
+ci = C.c_int
+
+_SIGNATURES = {
+    "b200_nvfp4_status_string": (C.c_char_p, [ci]),
+    "b200_nvfp4_gemm_path_string": (C.c_char_p, [ci]),
+    "b200_nvfp4_gemm_path": (ci, [ci, ci, ci]),
+    "b200_nvfp4_gemm_workspace_bytes": (C.c_size_t, [ci, ci, ci]),
+    "b200_nvfp4_gemm": (ci, [ci, ci, ci, ci, vp, vp, vp, vp, vp, ci, vp]),
+    "b200_nvfp4_gemm_splitk": (ci, [ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, C.c_size_t, vp]),
+    "b200_nvfp4_gemm_auto": (ci, [ci, ci, ci, vp, vp, vp, vp, vp, vp, C.c_size_t, vp]),
+    "b200_nvfp4_grouped_gemm": (ci, [vp] * 10 + [ci] * 7 + [vp, vp]),
+    "b200_nvfp4_moe_count_and_gather": (ci, [vp] * 8 + [ci] * 8 + [vp]),
+    "b200_nvfp4_moe_act_mul_and_quant": (ci, [vp] * 5 + [ci] * 5 + [vp]),
+    "b200_nvfp4_moe_quantize_expert": (ci, [vp] * 5 + [ci] * 6 + [vp]),
+    "b200_nvfp4_moe_reduce": (ci, [vp] * 5 + [ci] * 4 + [vp]),
+    "b200_nvfp4_fused_moe": (ci, [vp] * 23 + [ci] * 9 + [vp]),
+    "b200_nvfp4_expert_moe_workspace_bytes": (C.c_size_t, [ci] * 5),
+    "b200_nvfp4_expert_moe": (ci, [vp] * 10 + [C.c_size_t] + [ci] * 5 + [vp]),
+    "b200_nvfp4_device_error": (ci, [C.POINTER(ci)]),
+    "b200_nvfp4_set_tile_n": (ci, [ci]),
+    "b200_nvfp4_launch_count": (C.c_longlong, []),
+}
+
+
+def exported_symbols():
+    """Names every entry point include/b200_nvfp4.h declares."""
+    return sorted(_SIGNATURES)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            from . import build as _build
+            _build.build()
+        L = C.CDLL(str(_LIB_PATH))
+        for name, (restype, argtypes) in _SIGNATURES.items():
+            fn = getattr(L, name)  # AttributeError here = the library lacks a declared symbol
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = L
+    return _lib
+
+
+def status_string(status: int) -> str:
+    return lib().b200_nvfp4_status_string(status).decode()
+
+
+def check(status: int, what: str) -> None:
+    if status != STATUS_SUCCESS:
+        raise RuntimeError(f"{what} failed: {status_string(status)}")
+
+
+def device_error() -> int:
+    """Reads and clears the device-side error word (synchronises)."""
+    code = ci(0)
+    check(lib().b200_nvfp4_device_error(C.byref(code)), "b200_nvfp4_device_error")
+    return code.value
+
+
+def launch_count() -> int:
+    return int(lib().b200_nvfp4_launch_count())

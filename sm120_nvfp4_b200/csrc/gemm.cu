@@ -1,0 +1,423 @@
+// Host launchers and C ABI of the dense / batched / split-K / grouped NVFP4 GEMM.
+#include <atomic>
+#include <cstdint>
+#include <cstring>
+#include <mutex>
+
+#include <cuda_fp16.h>
+
+#include "gemm_kernel.cuh"
+#include "host_common.hpp"
+#include "internal.hpp"
+
+namespace b200 {
+
+__device__ int g_device_error = 0;
+
+int* device_error_word() {
+  constexpr int kMaxDevices = 64;
+  static int* cache[kMaxDevices] = {};
+  static std::mutex mu;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache[device] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_device_error) != cudaSuccess) return nullptr;
+    cache[device] = static_cast<int*>(ptr);
+  }
+  return cache[device];
+}
+
+std::atomic<long long> g_launch_count{0};
+
+std::atomic<int> g_tile_n_override{0};
+
+namespace {
+
+struct LaunchSpec {
+  int num_groups;
+  int m_uniform;           // rows per group (dense) - ignored when seqlens != nullptr
+  int a_rows_total;        // rows of the A matrix the tensor map covers
+  int n, k;
+  const void* a;
+  const void* b;
+  const void* sfa;
+  const void* sfb;
+  long long sfa_group_stride;
+  long long sfb_group_stride;
+  int b_group_rows;
+  int b_rows_total;
+  const int* seqlens;
+  const int* cu_seqlens;
+  void* out;
+  bool out_f32;
+  long long out_split_stride;
+  const float* group_alpha;
+  int num_splits;
+  int* tiles_out;
+  int* cu_tiles_out;
+  int expected_m_tiles;    // estimate used to pick the tile width and the grid
+  bool exact_m_tiles;      // expected_m_tiles is exact (dense) rather than a hint (grouped)
+};
+
+template <int BN, bool F32>
+int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  auto kernel = nvfp4_gemm_kernel<BN, F32>;
+  static std::once_flag once[64];
+  static cudaError_t attr_status[64];
+  std::call_once(once[dev.device], [&] {
+    attr_status[dev.device] = cudaFuncSetAttribute(
+        kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  });
+  if (attr_status[dev.device] != cudaSuccess) return B200_NVFP4_CUDA_ERROR;
+
+  CUtensorMap tmap_a, tmap_b;
+  const uint64_t row_bytes = static_cast<uint64_t>(s.k) / 2;
+  if (!encode_tmap_2d_u8(&tmap_a, s.a, static_cast<uint64_t>(s.a_rows_total), row_bytes, kBlockM,
+                         kStageKBytes, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !encode_tmap_2d_u8(&tmap_b, s.b, static_cast<uint64_t>(s.b_rows_total), row_bytes, BN,
+                         kStageKBytes, CU_TENSOR_MAP_SWIZZLE_128B)) {
+    return B200_NVFP4_CUDA_ERROR;
+  }
+
+  GemmParams p;
+  p.num_groups = s.num_groups;
+  p.n = s.n;
+  p.k = s.k;
+  p.m_uniform = s.m_uniform;
+  p.seqlens = s.seqlens;
+  p.cu_seqlens = s.cu_seqlens;
+  p.sfa = static_cast<const uint8_t*>(s.sfa);
+  p.sfb = static_cast<const uint8_t*>(s.sfb);
+  p.sfa_group_stride = s.sfa_group_stride;
+  p.sfb_group_stride = s.sfb_group_stride;
+  p.b_group_rows = s.b_group_rows;
+  p.out = s.out;
+  p.out_split_stride = s.out_split_stride;
+  p.group_alpha = s.group_alpha;
+  p.num_splits = s.num_splits;
+  p.raster_m = 16;
+  p.tiles_out = s.tiles_out;
+  p.cu_tiles_out = s.cu_tiles_out;
+  p.error = device_error_word();
+
+  const int n_tiles = (s.n + BN - 1) / BN;
+  long long tasks = static_cast<long long>(s.expected_m_tiles) * n_tiles * s.num_splits;
+  int grid = dev.sm_count;
+  if (s.exact_m_tiles && tasks < grid) grid = static_cast<int>(tasks);
+  if (grid < 1) grid = 1;
+  kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmap_a, tmap_b, p);
+  count_launch();
+  return cudaPeekAtLastError() == cudaSuccess ? B200_NVFP4_SUCCESS : B200_NVFP4_CUDA_ERROR;
+}
+
+// Tile width: 256 columns once there is at least a wave of such tiles (tensor-bound
+// shapes); otherwise the widest tile that still gives every SM a task, because skinny
+// problems are bound by streaming B from HBM and need all SMs pulling.
+int pick_tile_n(const LaunchSpec& s, const DeviceInfo& dev) {
+  const long long mt = s.expected_m_tiles > 0 ? s.expected_m_tiles : 1;
+  const long long splits = s.num_splits;
+  auto tasks = [&](int bn) { return mt * ((s.n + bn - 1) / bn) * splits; };
+  if (tasks(256) >= dev.sm_count) return 256;
+  if (tasks(128) >= dev.sm_count * 3 / 4) return 128;
+  if (tasks(64) >= dev.sm_count * 3 / 4 || s.n <= 64) return s.n <= 32 ? 32 : 64;
+  return 32;
+}
+
+int launch_gemm(const LaunchSpec& s, cudaStream_t stream, int force_tile_n = 0) {
+  const DeviceInfo& dev = current_device_info();
+  if (!dev.ok) return B200_NVFP4_CUDA_ERROR;
+  if (!device_supported(dev)) return B200_NVFP4_UNSUPPORTED_DEVICE;
+  const int bn = force_tile_n ? force_tile_n : pick_tile_n(s, dev);
+  switch (bn) {
+    case 256:
+      return s.out_f32 ? launch_instance<256, true>(s, dev, stream)
+                       : launch_instance<256, false>(s, dev, stream);
+    case 128:
+      return s.out_f32 ? launch_instance<128, true>(s, dev, stream)
+                       : launch_instance<128, false>(s, dev, stream);
+    case 64:
+      return s.out_f32 ? launch_instance<64, true>(s, dev, stream)
+                       : launch_instance<64, false>(s, dev, stream);
+    case 32:
+      return s.out_f32 ? launch_instance<32, true>(s, dev, stream)
+                       : launch_instance<32, false>(s, dev, stream);
+    default:
+      return B200_NVFP4_INVALID_ARGUMENT;
+  }
+}
+
+bool valid_shape(int m, int n, int k) {
+  return m > 0 && n > 0 && k > 0 && (k % 32) == 0 && (n % 8) == 0;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Tile-width override for tests and tuning (b200_nvfp4_set_tile_n); 0 = built-in choice.
+int env_tile_n() { return g_tile_n_override.load(std::memory_order_relaxed); }
+
+// out[i] = half(sum_s partial[s][i]), summed in split order with FP32 adds
+// (reduce_m128_splitk_kernel, src/gemm/specialized/m128_gemm.cu:367-382). numel % 8 == 0.
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ out,
+                                     long long numel8, long long split_stride, int splits) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < numel8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8];
+    const float4* src = reinterpret_cast<const float4*>(partial + i * 8);
+    float4 lo = src[0], hi = src[1];
+    acc[0] = lo.x; acc[1] = lo.y; acc[2] = lo.z; acc[3] = lo.w;
+    acc[4] = hi.x; acc[5] = hi.y; acc[6] = hi.z; acc[7] = hi.w;
+    for (int s = 1; s < splits; ++s) {
+      const float4* ps = reinterpret_cast<const float4*>(partial + s * split_stride + i * 8);
+      float4 a = ps[0], b = ps[1];
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    uint4 o;
+    o.x = pack_half2(acc[0], acc[1]);
+    o.y = pack_half2(acc[2], acc[3]);
+    o.z = pack_half2(acc[4], acc[5]);
+    o.w = pack_half2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + i * 8) = o;
+  }
+}
+
+}  // namespace
+
+int gemm_dense(int groups, int m, int n, int k, const void* a, const void* b, const void* sfa,
+               const void* sfb, void* c, bool out_f32, cudaStream_t stream) {
+  if (groups <= 0 || !valid_shape(m, n, k) || a == nullptr || b == nullptr || sfa == nullptr ||
+      sfb == nullptr || c == nullptr || groups > kMaxGroups || !aligned16(a) || !aligned16(b) ||
+      !aligned16(sfa) || !aligned16(sfb) || !aligned16(c)) {
+    return B200_NVFP4_INVALID_ARGUMENT;
+  }
+  const int skp = scale_k_padded(k);
+  LaunchSpec s{};
+  s.num_groups = groups;
+  s.m_uniform = m;
+  s.a_rows_total = groups * m;
+  s.n = n;
+  s.k = k;
+  s.a = a;
+  s.b = b;
+  s.sfa = sfa;
+  s.sfb = sfb;
+  s.sfa_group_stride = static_cast<long long>(align_up_int(m, 128)) * skp;
+  s.sfb_group_stride = static_cast<long long>(align_up_int(n, 128)) * skp;
+  s.b_group_rows = n;
+  s.b_rows_total = groups * n;
+  s.out = c;
+  s.out_f32 = out_f32;
+  s.out_split_stride = 0;
+  s.num_splits = 1;
+  s.expected_m_tiles = groups * ((m + kBlockM - 1) / kBlockM);
+  s.exact_m_tiles = true;
+  return launch_gemm(s, stream, env_tile_n());
+}
+
+int gemm_splitk(int m, int n, int k, int split_k, const void* a, const void* b, const void* sfa,
+                const void* sfb, void* c_f16, void* workspace, size_t workspace_bytes,
+                cudaStream_t stream) {
+  if (!valid_shape(m, n, k) || split_k < 1 || split_k > (k + 127) / 128 || a == nullptr ||
+      b == nullptr || sfa == nullptr || sfb == nullptr || c_f16 == nullptr ||
+      workspace == nullptr || !aligned16(workspace) || !aligned16(a) || !aligned16(b) ||
+      !aligned16(sfa) || !aligned16(sfb) || !aligned16(c_f16)) {
+    return B200_NVFP4_INVALID_ARGUMENT;
+  }
+  const size_t required = static_cast<size_t>(split_k) * m * n * sizeof(float);
+  if (workspace_bytes < required) return B200_NVFP4_INSUFFICIENT_WORKSPACE;
+  const int skp = scale_k_padded(k);
+  LaunchSpec s{};
+  s.num_groups = 1;
+  s.m_uniform = m;
+  s.a_rows_total = m;
+  s.n = n;
+  s.k = k;
+  s.a = a;
+  s.b = b;
+  s.sfa = sfa;
+  s.sfb = sfb;
+  s.sfa_group_stride = static_cast<long long>(align_up_int(m, 128)) * skp;
+  s.sfb_group_stride = static_cast<long long>(align_up_int(n, 128)) * skp;
+  s.b_group_rows = n;
+  s.b_rows_total = n;
+  s.out = workspace;
+  s.out_f32 = true;
+  s.out_split_stride = static_cast<long long>(m) * n;
+  s.num_splits = split_k;
+  s.expected_m_tiles = (m + kBlockM - 1) / kBlockM;
+  s.exact_m_tiles = true;
+  int status = launch_gemm(s, stream, env_tile_n());
+  if (status != B200_NVFP4_SUCCESS) return status;
+  const DeviceInfo& dev = current_device_info();
+  const long long numel8 = static_cast<long long>(m) * n / 8;
+  long long blocks = (numel8 + 255) / 256;
+  if (blocks > static_cast<long long>(dev.sm_count) * 8) blocks = static_cast<long long>(dev.sm_count) * 8;
+  splitk_reduce_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+      static_cast<const float*>(workspace), static_cast<__half*>(c_f16), numel8,
+      static_cast<long long>(m) * n, split_k);
+  count_launch();
+  return cudaPeekAtLastError() == cudaSuccess ? B200_NVFP4_SUCCESS : B200_NVFP4_CUDA_ERROR;
+}
+
+int gemm_grouped(void* y, const void* x, const void* w, const void* seqlens,
+                 const void* cu_seqlens, const void* x_scale, const void* w_scale, void* tiles,
+                 void* cu_tiles, int num_group, int m, int n, int k, int m_scale_pad,
+                 int num_seq_per_group_avg, const float* group_alpha, cudaStream_t stream) {
+  if (num_group <= 0 || num_group > kMaxGroups || !valid_shape(m, n, k) || y == nullptr ||
+      x == nullptr || w == nullptr || seqlens == nullptr || cu_seqlens == nullptr ||
+      x_scale == nullptr || w_scale == nullptr || m_scale_pad < 128 || (m_scale_pad % 128) != 0 ||
+      !aligned16(y) || !aligned16(x) || !aligned16(w) || !aligned16(x_scale) ||
+      !aligned16(w_scale)) {
+    return B200_NVFP4_INVALID_ARGUMENT;
+  }
+  const int skp = scale_k_padded(k);
+  LaunchSpec s{};
+  s.num_groups = num_group;
+  s.m_uniform = 0;
+  s.a_rows_total = m;
+  s.n = n;
+  s.k = k;
+  s.a = x;
+  s.b = w;
+  s.sfa = x_scale;
+  s.sfb = w_scale;
+  s.sfa_group_stride = static_cast<long long>(m_scale_pad) * skp;
+  s.sfb_group_stride = static_cast<long long>(align_up_int(n, 128)) * skp;
+  s.b_group_rows = n;
+  s.b_rows_total = num_group * n;
+  s.seqlens = static_cast<const int*>(seqlens);
+  s.cu_seqlens = static_cast<const int*>(cu_seqlens);
+  s.out = y;
+  s.out_f32 = false;
+  s.num_splits = 1;
+  s.group_alpha = group_alpha;
+  s.tiles_out = static_cast<int*>(tiles);
+  s.cu_tiles_out = static_cast<int*>(cu_tiles);
+  // Row counts live on the device; estimate the m-tiles for the tile-width heuristic only.
+  int avg = num_seq_per_group_avg > 0 ? num_seq_per_group_avg : (m + num_group - 1) / num_group;
+  long long est = static_cast<long long>(num_group) * ((avg + kBlockM - 1) / kBlockM);
+  long long upper = static_cast<long long>(m) / kBlockM + num_group;
+  if (est > upper) est = upper;
+  if (est < 1) est = 1;
+  s.expected_m_tiles = static_cast<int>(est);
+  s.exact_m_tiles = false;
+  return launch_gemm(s, stream, env_tile_n());
+}
+
+}  // namespace b200
+
+// --------------------------------------------------------------------------- C ABI
+
+extern "C" {
+
+const char* b200_nvfp4_status_string(int status) {
+  switch (status) {
+    case B200_NVFP4_SUCCESS: return "success";
+    case B200_NVFP4_INVALID_ARGUMENT: return "invalid argument or unsupported alignment";
+    case B200_NVFP4_UNSUPPORTED_DEVICE: return "current device is not SM100 (B200)";
+    case B200_NVFP4_INSUFFICIENT_WORKSPACE: return "workspace is null or too small";
+    case B200_NVFP4_CUTLASS_NOT_SUPPORTED: return "CUTLASS cannot implement this problem shape/alignment";
+    case B200_NVFP4_CUTLASS_ERROR: return "CUTLASS initialize or launch failed";
+    case B200_NVFP4_CUDA_ERROR: return "CUDA runtime error";
+  }
+  return "unknown status";
+}
+
+const char* b200_nvfp4_gemm_path_string(int path) {
+  switch (path) {
+    case B200_NVFP4_PATH_GENERIC: return "generic_cute";
+    case B200_NVFP4_PATH_M128_SPLITK4: return "m128_splitk4";
+    case B200_NVFP4_PATH_M256_SPLITK2: return "m256_splitk2";
+  }
+  return "unknown";
+}
+
+int b200_nvfp4_gemm_path(int m, int n, int k) {
+  const bool shape_ok = n > 0 && k > 0 && (k % 32) == 0 && (n % 8) == 0;
+  const int tiles_k = (k + 127) / 128;
+  if (m == 128 && shape_ok && 4 <= tiles_k) return B200_NVFP4_PATH_M128_SPLITK4;
+  if (m == 256 && shape_ok && 2 <= tiles_k) return B200_NVFP4_PATH_M256_SPLITK2;
+  return B200_NVFP4_PATH_GENERIC;
+}
+
+size_t b200_nvfp4_gemm_workspace_bytes(int m, int n, int k) {
+  switch (b200_nvfp4_gemm_path(m, n, k)) {
+    case B200_NVFP4_PATH_M128_SPLITK4: return static_cast<size_t>(4) * m * n * sizeof(float);
+    case B200_NVFP4_PATH_M256_SPLITK2: return static_cast<size_t>(2) * m * n * sizeof(float);
+    default: return 0;
+  }
+}
+
+int b200_nvfp4_gemm(int groups, int m, int n, int k, const void* a, const void* b, const void* sfa,
+                    const void* sfb, void* c, int out_is_f32, b200_stream_t stream) {
+  return b200::gemm_dense(groups, m, n, k, a, b, sfa, sfb, c, out_is_f32 != 0,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int b200_nvfp4_gemm_splitk(int m, int n, int k, int split_k, const void* a, const void* b,
+                           const void* sfa, const void* sfb, void* c_f16, void* workspace,
+                           size_t workspace_bytes, b200_stream_t stream) {
+  return b200::gemm_splitk(m, n, k, split_k, a, b, sfa, sfb, c_f16, workspace, workspace_bytes,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int b200_nvfp4_gemm_auto(int m, int n, int k, const void* a, const void* b, const void* sfa,
+                         const void* sfb, void* c_f16, void* workspace, size_t workspace_bytes,
+                         b200_stream_t stream) {
+  const int path = b200_nvfp4_gemm_path(m, n, k);
+  const size_t required = b200_nvfp4_gemm_workspace_bytes(m, n, k);
+  if (required != 0 && (workspace == nullptr || workspace_bytes < required))
+    return B200_NVFP4_INSUFFICIENT_WORKSPACE;
+  switch (path) {
+    case B200_NVFP4_PATH_M128_SPLITK4:
+      return b200_nvfp4_gemm_splitk(m, n, k, 4, a, b, sfa, sfb, c_f16, workspace, workspace_bytes, stream);
+    case B200_NVFP4_PATH_M256_SPLITK2:
+      return b200_nvfp4_gemm_splitk(m, n, k, 2, a, b, sfa, sfb, c_f16, workspace, workspace_bytes, stream);
+    default:
+      return b200_nvfp4_gemm(1, m, n, k, a, b, sfa, sfb, c_f16, 0, stream);
+  }
+}
+
+int b200_nvfp4_grouped_gemm(void* y, const void* x, const void* w, const void* seqlens,
+                            const void* cu_seqlens, const void* x_scale, const void* w_scale,
+                            void* tmas, void* tiles, void* cu_tiles, int num_group, int m, int n,
+                            int k, int m_scale_pad, int num_seq_per_group_avg, int update_tma,
+                            const float* group_alpha, b200_stream_t stream) {
+  (void)tmas;
+  (void)update_tma;
+  return b200::gemm_grouped(y, x, w, seqlens, cu_seqlens, x_scale, w_scale, tiles, cu_tiles,
+                            num_group, m, n, k, m_scale_pad, num_seq_per_group_avg, group_alpha,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int b200_nvfp4_device_error(int* code) {
+  int* word = b200::device_error_word();
+  if (word == nullptr || code == nullptr) return B200_NVFP4_CUDA_ERROR;
+  int value = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return B200_NVFP4_CUDA_ERROR;
+  if (cudaMemcpy(&value, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+    return B200_NVFP4_CUDA_ERROR;
+  if (value != 0) {
+    int zero = 0;
+    if (cudaMemcpy(word, &zero, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess)
+      return B200_NVFP4_CUDA_ERROR;
+  }
+  *code = value;
+  return B200_NVFP4_SUCCESS;
+}
+
+int b200_nvfp4_set_tile_n(int tile_n) {
+  if (tile_n != 0 && tile_n != 32 && tile_n != 64 && tile_n != 128 && tile_n != 256)
+    return B200_NVFP4_INVALID_ARGUMENT;
+  b200::g_tile_n_override.store(tile_n, std::memory_order_relaxed);
+  return B200_NVFP4_SUCCESS;
+}
+
+long long b200_nvfp4_launch_count(void) {
+  return b200::g_launch_count.load(std::memory_order_relaxed);
+}
+
+}  // extern "C"

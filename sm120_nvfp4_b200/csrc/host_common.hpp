@@ -1,0 +1,40 @@
+// Host-side helpers shared by the launchers: status codes of the C ABI, cached device
+// properties, the driver entry point for tensor-map encoding and the device error word.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "b200_nvfp4.h"
+
+namespace b200 {
+
+struct DeviceInfo {
+  int device = -1;
+  int sm_count = 0;
+  int cc_major = 0;
+  int cc_minor = 0;
+  bool ok = false;
+};
+
+// Properties of the current device (queried once per device, then cached).
+const DeviceInfo& current_device_info();
+
+// True when the current device can run the sm_100a kernels (compute capability 10.x).
+bool device_supported(const DeviceInfo& info);
+
+// Encodes a rank-2 tiled tensor map over a row-major byte matrix [rows, row_bytes] with a
+// box of [box_rows, box_bytes] and the given swizzle. Returns false on failure.
+bool encode_tmap_2d_u8(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                       uint32_t box_rows, uint32_t box_bytes, CUtensorMapSwizzle swizzle);
+
+// Device word written by kernels whose bounded waits time out. One per loaded library.
+int* device_error_word();
+
+inline int align_up_int(int x, int a) { return (x + a - 1) / a * a; }
+inline int scale_k_padded(int k) { return align_up_int((k + 15) / 16, 4); }
+
+}  // namespace b200

@@ -1,0 +1,262 @@
+"""GPU parity tests of the fused-MoE path: routing, gather, SiLU*up + quantisation, row
+quantisation, weighted reduce, the two fused entry points - against the CPU oracle and the
+reference's known answers. Gates: routing permutation and offsets bit-exact, UE4M3 scales
+bit-exact, E2M1 codes >= 99.9 % identical, GEMM-backed outputs within the GEMM gate."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import check_gemm_parity, randn_quantized, topk_routing
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import sm120_nvfp4_b200 as pkg
+    from sm120_nvfp4_b200 import _lib
+    _lib.lib()
+    yield pkg
+    assert _lib.device_error() == 0
+
+
+def _dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def make_case():
+    tokens, experts, hidden, inter = 4, 2, 128, 64
+    x = torch.full((tokens, hidden // 2), 0x11, dtype=torch.uint8, device="cuda")
+    gw = torch.full((experts, 2 * inter, hidden // 2), 0x11, dtype=torch.uint8, device="cuda")
+    dw = torch.full((experts, hidden, inter // 2), 0x11, dtype=torch.uint8, device="cuda")
+    xs = torch.full((128 * 8,), 0x38, dtype=torch.uint8, device="cuda")
+    gs = torch.full((experts, 128 * 8), 0x38, dtype=torch.uint8, device="cuda")
+    ds = torch.full((experts, 128 * 4), 0x38, dtype=torch.uint8, device="cuda")
+    return tokens, experts, hidden, x, xs, gw, gs, dw, ds
+
+
+def test_uniform_data(ops):
+    # tests/python/test_fused_moe.py:55-101
+    tokens, experts, hidden, x, xs, gw, gs, dw, ds = make_case()
+    ids = torch.tensor([[0, 1], [1, 0], [0, 1], [1, 0]], dtype=torch.int32, device="cuda")
+    w = torch.tensor([[0.25, 0.75], [0.6, 0.4], [0.5, 0.5], [0.2, 0.8]], dtype=torch.float32, device="cuda")
+    shared = torch.full((tokens, hidden), 2.0, dtype=torch.float16, device="cuda")
+    output = torch.empty_like(shared)
+    result = ops.fused_moe(x, xs, gw, gs, dw, ds, ids, w, shared_output=shared, output=output)
+    torch.cuda.synchronize()
+    assert result.data_ptr() == output.data_ptr()
+    assert (result.float() == 33792.0).all(), result.float().unique()
+
+
+def test_nonlocal_routes_are_ignored(ops):
+    # tests/python/test_fused_moe.py:103-140
+    tokens, _, hidden, x, xs, gw, gs, dw, ds = make_case()
+    ids = torch.full((tokens, 1), 2, dtype=torch.int32, device="cuda")
+    w = torch.ones((tokens, 1), dtype=torch.float32, device="cuda")
+    shared = torch.full((tokens, hidden), 2.0, dtype=torch.float16, device="cuda")
+    result = ops.fused_moe(x, xs, gw, gs, dw, ds, ids, w, shared_output=shared, ep_rank=0, num_experts=4)
+    assert torch.equal(result, shared)
+
+
+def test_nonuniform_activation_scales_survive_routing(ops):
+    # tests/python/test_fused_moe.py:142-195
+    tokens, experts, _, x, xs, gw, gs, dw, ds = make_case()
+    scale = torch.zeros_like(xs)
+    for row, code in enumerate((0x30, 0x38, 0x30, 0x38)):
+        for kb in range(8):
+            scale[(kb // 4) * 512 + (row % 32) * 16 + (row // 32) * 4 + (kb % 4)] = code
+    ids = torch.tensor([[1], [0], [1], [0]], dtype=torch.int32, device="cuda")
+    w = torch.ones((tokens, 1), dtype=torch.float32, device="cuda")
+    result = ops.fused_moe(x, scale, gw, gs, dw, ds, ids, w, num_experts=experts)
+    assert result[:, 0].float().cpu().tolist() == [8448.0, 33792.0, 8448.0, 33792.0]
+
+
+def test_expert_major_handoff_matches_reroute(ops):
+    # tests/python/test_fused_moe.py:198-300
+    rows, experts, hidden, inter = 5, 2, 128, 64
+    torch.manual_seed(7)
+    x = (torch.randn(rows, hidden, dtype=torch.bfloat16, device="cuda") * 0.25).contiguous()
+    seqlens = torch.tensor([2, 3], dtype=torch.int32, device="cuda")
+    cu = torch.tensor([0, 2, 5], dtype=torch.int32, device="cuda")
+    packed, scales = ops.quantize_expert(x, seqlens, cu, scale_m_pad=128)
+    gw = torch.full((experts, 2 * inter, hidden // 2), 0x11, dtype=torch.uint8, device="cuda")
+    dw = torch.full((experts, hidden, inter // 2), 0x11, dtype=torch.uint8, device="cuda")
+    gs = torch.full((experts, 128 * ops.scale_k_padded(hidden)), 0x38, dtype=torch.uint8, device="cuda")
+    ds = torch.full((experts, 128 * ops.scale_k_padded(inter)), 0x38, dtype=torch.uint8, device="cuda")
+    ws_bytes = ops.expert_moe_workspace_bytes(rows, hidden, inter, experts, 128)
+    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+    direct_out = torch.empty(rows, hidden, dtype=torch.float16, device="cuda")
+    direct = ops.expert_moe(packed, scales, gw, gs, dw, ds, seqlens, cu, output=direct_out, workspace=workspace)
+    one_len = torch.tensor([rows], dtype=torch.int32, device="cuda")
+    one_cu = torch.tensor([0, rows], dtype=torch.int32, device="cuda")
+    base_in, base_scale = ops.quantize_expert(x, one_len, one_cu, scale_m_pad=128)
+    ids = torch.tensor([[0], [0], [1], [1], [1]], dtype=torch.int32, device="cuda")
+    w = torch.ones(rows, 1, dtype=torch.float32, device="cuda")
+    baseline = ops.fused_moe(base_in, base_scale.flatten(), gw, gs, dw, ds, ids, w)
+    torch.cuda.synchronize()
+    assert direct.data_ptr() == direct_out.data_ptr()
+    assert torch.equal(direct, baseline)
+    # and both agree with the oracle on the same input bits
+    xb = x.view(torch.int16).cpu().numpy().view(np.uint16)
+    o_packed, o_scales = oracle.quantize_expert(xb, [2, 3], [0, 2, 5], 128, True)
+    np.testing.assert_array_equal(packed.cpu().numpy(), o_packed)
+    np.testing.assert_array_equal(scales.cpu().numpy(), o_scales)
+    want = oracle.expert_moe(o_packed, o_scales, gw.cpu().numpy(), gs.cpu().numpy(), dw.cpu().numpy(),
+                             ds.cpu().numpy(), [2, 3], [0, 2, 5], 128)
+    np.testing.assert_array_equal(direct.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("tokens,experts,topk,rank_ep,local", [
+    (4, 2, 2, 0, 2), (1, 256, 8, 0, 256), (300, 16, 4, 1, 8), (4096, 256, 8, 0, 256),
+    (4096, 256, 8, 3, 32), (5000, 64, 6, 0, 64), (256, 8, 8, 0, 8)])
+def test_routing_and_gather_bit_exact(ops, tokens, experts, topk, rank_ep, local):
+    from sm120_nvfp4_b200 import _lib
+    L = _lib.lib()
+    hidden = 256
+    ids, _ = topk_routing(tokens, experts, topk, 40 + tokens)
+    if tokens == 256:  # every token to every expert: heavy collisions
+        ids = np.tile(np.arange(8, dtype=np.int32), (tokens, 1))
+    x, xs = randn_quantized(tokens, hidden, 41 + tokens)
+    in_pad = (tokens + 127) // 128 * 128
+    total = tokens * topk
+    m_pad = max(128, (total + 127) // 128 * 128)
+    if total > 20000:
+        m_pad = 4096  # keeps the scale buffers of the test small; counts stay below it
+    o_gin, o_gscale, o_pos, o_seq, o_cu = oracle.count_and_gather(x, xs, ids, local, rank_ep, in_pad, m_pad)
+    assert o_seq.max() <= m_pad
+    skp = oracle.scale_k_padded(hidden)
+    gin = torch.zeros((total, hidden // 2), dtype=torch.uint8, device="cuda")
+    gscale = torch.full((local, m_pad * skp), 0xAB, dtype=torch.uint8, device="cuda")
+    pos = torch.full((tokens, topk), -7, dtype=torch.int32, device="cuda")
+    seq = torch.full((local,), -7, dtype=torch.int32, device="cuda")
+    cu = torch.full((local + 1,), -7, dtype=torch.int32, device="cuda")
+    dx, dxs, dids = _dev(x), _dev(xs), _dev(ids)
+    st = L.b200_nvfp4_moe_count_and_gather(gin.data_ptr(), gscale.data_ptr(), dx.data_ptr(), dxs.data_ptr(),
+                                           dids.data_ptr(), pos.data_ptr(), seq.data_ptr(), cu.data_ptr(),
+                                           tokens, hidden, topk, local, rank_ep, in_pad, m_pad, 1, _stream())
+    assert st == 0
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(seq.cpu().numpy(), o_seq)
+    np.testing.assert_array_equal(cu.cpu().numpy(), o_cu)
+    np.testing.assert_array_equal(pos.cpu().numpy(), o_pos)
+    np.testing.assert_array_equal(gin.cpu().numpy(), o_gin)
+    np.testing.assert_array_equal(gscale.cpu().numpy(), o_gscale)
+    assert _lib.device_error() == 0
+
+
+@pytest.mark.parametrize("inter", [64, 2048, 96])
+def test_act_mul_and_quant_parity(ops, inter):
+    from sm120_nvfp4_b200 import _lib
+    L = _lib.lib()
+    counts = np.array([3, 0, 130, 70], np.int32)
+    cu = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    rows, e, m_pad = int(cu[-1]), len(counts), 256
+    rng = np.random.default_rng(inter)
+    gate_up = (rng.standard_normal((rows, 2 * inter)) * 2.0).astype(np.float16)
+    gate_up[0, :16] = 0  # a zero block
+    gate_up[1, :] *= np.float16(1e-3)
+    gate_up[2, :inter] = np.float16(-30.0)  # silu underflow region
+    o_out, o_scale = oracle.act_mul_and_quant(gate_up, counts, cu, m_pad)
+    out = torch.zeros((rows, inter // 2), dtype=torch.uint8, device="cuda")
+    scale = torch.full((e, m_pad * oracle.scale_k_padded(inter)), 0xCD, dtype=torch.uint8, device="cuda")
+    dg, dc, dcu = _dev(gate_up), _dev(counts), _dev(cu)
+    st = L.b200_nvfp4_moe_act_mul_and_quant(out.data_ptr(), scale.data_ptr(), dg.data_ptr(), dc.data_ptr(),
+                                            dcu.data_ptr(), e, rows, m_pad, inter, 1, _stream())
+    assert st == 0
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(scale.cpu().numpy(), o_scale)  # UE4M3 scales bit-exact
+    got = out.cpu().numpy()
+    same = ((got & 15) == (o_out & 15)).sum() + ((got >> 4) == (o_out >> 4)).sum()
+    assert same / (2 * got.size) >= 0.999
+    assert _lib.device_error() == 0
+
+
+@pytest.mark.parametrize("is_bf16", [True, False])
+def test_quantize_expert_parity(ops, golden_dir, is_bf16):
+    g = np.load(golden_dir / "quantizer.npz")
+    bits = g["input_bf16_bits"]
+    rows, hidden = bits.shape
+    if is_bf16:
+        x = torch.from_numpy(bits.view(np.int16)).cuda().view(torch.bfloat16)
+        host_bits = bits
+    else:
+        rng = np.random.default_rng(5)
+        xf = (rng.standard_normal((rows, hidden)) * 3).astype(np.float16)
+        xf[0, :16] = 0
+        x = torch.from_numpy(xf).cuda()
+        host_bits = xf.view(np.uint16)
+    counts = np.array([10, 0, rows - 10], np.int32)
+    cu = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    packed, scales = ops.quantize_expert(x, _dev(counts), _dev(cu), scale_m_pad=128)
+    o_packed, o_scales = oracle.quantize_expert(host_bits, counts, cu, 128, is_bf16)
+    np.testing.assert_array_equal(scales.cpu().numpy(), o_scales)
+    np.testing.assert_array_equal(packed.cpu().numpy(), o_packed)
+
+
+@pytest.mark.parametrize("with_shared", [True, False])
+def test_reduce_bit_exact(ops, with_shared):
+    from sm120_nvfp4_b200 import _lib
+    L = _lib.lib()
+    tokens, topk, hidden, rows = 37, 8, 512, 200
+    rng = np.random.default_rng(9)
+    down = (rng.standard_normal((rows, hidden)) * 4).astype(np.float16)
+    pos = rng.integers(-1, rows, size=(tokens, topk)).astype(np.int32)
+    w = rng.random((tokens, topk)).astype(np.float32)
+    shared = (rng.standard_normal((tokens, hidden))).astype(np.float16) if with_shared else None
+    want = oracle.reduce(down, pos, w, shared)
+    out = torch.empty((tokens, hidden), dtype=torch.float16, device="cuda")
+    dd, dp, dw = _dev(down), _dev(pos), _dev(w)
+    ds = _dev(shared) if with_shared else None
+    st = L.b200_nvfp4_moe_reduce(out.data_ptr(), dd.data_ptr(), dp.data_ptr(), dw.data_ptr(),
+                                 None if ds is None else ds.data_ptr(), tokens, hidden, topk, 0, _stream())
+    assert st == 0
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(out.cpu().numpy(), want)
+
+
+def _moe_weights(experts, hidden, inter, seed, std=0.02):
+    gw = np.empty((experts, 2 * inter, hidden // 2), np.uint8)
+    gs = np.empty((experts, oracle.scale_region_bytes(2 * inter, hidden)), np.uint8)
+    dw = np.empty((experts, hidden, inter // 2), np.uint8)
+    ds = np.empty((experts, oracle.scale_region_bytes(hidden, inter)), np.uint8)
+    for e in range(experts):
+        gw[e], gs[e] = randn_quantized(2 * inter, hidden, seed + 2 * e, std)
+        dw[e], ds[e] = randn_quantized(hidden, inter, seed + 2 * e + 1, std)
+    return gw, gs, dw, ds
+
+
+@pytest.mark.parametrize("tokens,experts,topk,hidden,inter,rank_ep,local", [
+    (64, 8, 2, 256, 128, 0, 8), (200, 16, 4, 512, 256, 1, 8), (33, 4, 4, 128, 64, 0, 4)])
+def test_full_moe_random_vs_oracle(ops, tokens, experts, topk, hidden, inter, rank_ep, local):
+    rng = np.random.default_rng(tokens)
+    L = oracle.lib()
+    xb = np.array([L.oracle_f32_to_bf16(float(v)) for v in rng.standard_normal(tokens * hidden)],
+                  np.uint16).reshape(tokens, hidden)
+    in_pad = (tokens + 127) // 128 * 128
+    x, xs = oracle.quantize_expert(xb, [tokens], [0, tokens], in_pad, True)
+    gw, gs, dw, ds = _moe_weights(local, hidden, inter, 700 + tokens, std=0.5)
+    ids, w = topk_routing(tokens, experts, topk, 50 + tokens)
+    shared = rng.standard_normal((tokens, hidden)).astype(np.float16)
+    want, o_pos, o_seq, o_cu = oracle.fused_moe(x, xs.ravel(), gw, gs, dw, ds, ids, w, shared, rank_ep=rank_ep)
+    # same quantisation on the GPU, bit for bit
+    xt = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+    gx, gxs = ops.quantize_expert(xt, _dev(np.array([tokens], np.int32)), _dev(np.array([0, tokens], np.int32)),
+                                  scale_m_pad=in_pad)
+    np.testing.assert_array_equal(gx.cpu().numpy(), x)
+    np.testing.assert_array_equal(gxs.cpu().numpy(), xs)
+    out = ops.fused_moe(gx, gxs.flatten(), _dev(gw), _dev(gs), _dev(dw), _dev(ds), _dev(ids), _dev(w),
+                        shared_output=_dev(shared), ep_rank=rank_ep, num_experts=experts)
+    got = out.cpu().numpy()
+    # end to end the two sides re-quantise FP16 intermediates that may differ in the last bit,
+    # so the layer output is held to a relative-Frobenius gate of 2e-2 (the reference's own
+    # analytic check uses rtol .02 / RMSE .003, docs/OPERATOR_MILESTONE.md:103-116)
+    num = np.linalg.norm(got.astype(np.float64) - want.astype(np.float64))
+    den = np.linalg.norm(want.astype(np.float64))
+    assert np.isfinite(got).all() and num / den < 2e-2, num / den

@@ -1,0 +1,208 @@
+"""GPU parity tests of the NVFP4 GEMM (dense, batched, FP32, split-K) against the CPU oracle
+and the committed golden vectors. All calls go through the C ABI (via the Python ops)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import check_gemm_parity, randn_quantized
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import sm120_nvfp4_b200 as pkg
+    from sm120_nvfp4_b200 import _lib
+    _lib.lib()  # must load: there is no fallback path
+    yield pkg
+    _lib.lib().b200_nvfp4_set_tile_n(0)
+    assert _lib.device_error() == 0
+
+
+def _dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+def _no_device_error():
+    from sm120_nvfp4_b200 import _lib
+    assert _lib.device_error() == 0, "a bounded wait inside a kernel timed out"
+
+
+def _ones_case(ops, fn, m, n, k):
+    a = torch.full((m, k // 2), 0x22, dtype=torch.uint8, device="cuda")
+    b = torch.full((n, k // 2), 0x22, dtype=torch.uint8, device="cuda")
+    sfa = torch.full((ops.scale_a_elements(m, n, k),), 0x38, dtype=torch.uint8, device="cuda")
+    sfb = torch.full((ops.scale_b_elements(m, n, k),), 0x38, dtype=torch.uint8, device="cuda")
+    out = fn(a, b, sfa, sfb)
+    torch.cuda.synchronize()
+    assert out.dtype == torch.float16 and tuple(out.shape) == (m, n)
+    got = out.float().cpu().numpy()
+    assert (got == float(k)).all(), f"{fn.__name__} m={m} n={n} k={k}: {np.unique(got)[:8]}"
+
+
+@pytest.mark.parametrize("tile_n", [0, 32, 64, 128, 256])
+def test_all_ones_known_answer(ops, tile_n):
+    # tests/python/test_gemm.py:39-68,102-134 (+ K tails and every tile width)
+    from sm120_nvfp4_b200 import _lib
+    _lib.lib().b200_nvfp4_set_tile_n(tile_n)
+    for m, n, k in ((16, 128, 128), (64, 136, 128), (129, 136, 128), (128, 128, 64), (8, 8, 32),
+                    (130, 264, 96), (16, 512, 1024), (300, 520, 2080)):
+        _ones_case(ops, ops.cute_gemm, m, n, k)
+        _ones_case(ops, ops.gemm, m, n, k)
+        _ones_case(ops, ops.cutlass_gemm, m, n, k)
+    _no_device_error()
+
+
+def test_specialized_dispatch_matches_generic(ops):
+    # tests/python/test_gemm.py:70-100: M=128 / 256, N=128, K=512 (more splits than k-stages)
+    for m in (128, 256):
+        _ones_case(ops, ops.gemm, m, 128, 512)
+        _ones_case(ops, ops.cute_gemm, m, 128, 512)
+    _no_device_error()
+
+
+@pytest.mark.parametrize("tile_n", [0, 32, 64, 128, 256])
+def test_dyadic_random_payloads_exact(ops, golden_dir, tile_n):
+    # tests/python/test_gemm.py:17-37: exact equality with the dequantised matmul
+    from sm120_nvfp4_b200 import _lib
+    _lib.lib().b200_nvfp4_set_tile_n(tile_n)
+    g = np.load(golden_dir / "dyadic_gemm.npz")
+    n, k = 256, 512
+    for m in (7, 128, 256):
+        a, b = _dev(g[f"a_{m}"]), _dev(g[f"b_{m}"])
+        sfa = torch.full((ops.scale_a_elements(m, n, k),), 0x18, dtype=torch.uint8, device="cuda")
+        sfb = torch.full((ops.scale_b_elements(m, n, k),), 0x20, dtype=torch.uint8, device="cuda")
+        for fn in (ops.gemm, ops.cute_gemm):
+            got = fn(a, b, sfa, sfb).cpu().numpy()
+            np.testing.assert_array_equal(got, g[f"expected_{m}"], err_msg=f"{fn.__name__} m={m}")
+    _no_device_error()
+
+
+def _random_case(m, n, k, seed):
+    a, sfa = randn_quantized(m, k, seed)
+    b, sfb = randn_quantized(n, k, seed + 1)
+    return a, sfa, b, sfb
+
+
+@pytest.mark.parametrize("tile_n", [0, 32, 64, 128, 256])
+@pytest.mark.parametrize("shape", [(16, 256, 512), (200, 328, 1056), (77, 40, 96), (128, 512, 2048)])
+def test_random_scales_vs_oracle(ops, shape, tile_n):
+    # non-uniform per-block scales: exercises the scale layout end to end
+    from sm120_nvfp4_b200 import _lib
+    _lib.lib().b200_nvfp4_set_tile_n(tile_n)
+    m, n, k = shape
+    a, sfa, b, sfb = _random_case(m, n, k, 100 + m)
+    ref32, _ = oracle.gemm(a, b, sfa, sfb)
+    for fn in (ops.cute_gemm, ops.gemm):
+        got = fn(_dev(a), _dev(b), _dev(sfa), _dev(sfb)).cpu().numpy()
+        check_gemm_parity(got, ref32)
+    _no_device_error()
+
+
+def test_config1_full_vs_oracle(ops):
+    # M=16, N=4096, K=8192: the reference's CPU-reference shape, compared in full
+    m, n, k = 16, 4096, 8192
+    a, sfa, b, sfb = _random_case(m, n, k, 0xB2000100)
+    ref32, _ = oracle.gemm(a, b, sfa, sfb)
+    got = ops.gemm(_dev(a), _dev(b), _dev(sfa), _dev(sfb)).cpu().numpy()
+    frob, worst = check_gemm_parity(got, ref32)
+    print(f"C1 frob={frob:.2e} gate={worst:.3f}")
+    _no_device_error()
+
+
+@pytest.mark.parametrize("m", [128, 256, 1024, 4096])
+def test_config2_m_sweep_sampled(ops, m):
+    # N=4096, K=8192; M=128/256 take the split-K paths. Oracle on sampled rows x columns.
+    n, k = 4096, 8192
+    a, sfa, b, sfb = _random_case(m, n, k, 0xB2000200 + m)
+    rng = np.random.default_rng(m)
+    rows = np.sort(rng.choice(m, size=min(m, 24), replace=False)).astype(np.int32)
+    cols = np.sort(rng.choice(n, size=384, replace=False)).astype(np.int32)
+    ref = oracle.gemm_sampled(a, b, sfa, sfb, rows, cols)
+    out = ops.gemm(_dev(a), _dev(b), _dev(sfa), _dev(sfb))
+    got = out.cpu().numpy()[np.ix_(rows, cols)]
+    check_gemm_parity(got, ref)
+    if m in (128, 256):  # dispatcher and generic kernel agree within the gate as well
+        got2 = ops.cute_gemm(_dev(a), _dev(b), _dev(sfa), _dev(sfb)).cpu().numpy()[np.ix_(rows, cols)]
+        check_gemm_parity(got2, ref)
+    _no_device_error()
+
+
+def test_square_8192_sampled_and_linearity(ops):
+    # full-size property checks: sampled oracle comparison, and doubling every A scale
+    # (adding 8 to the UE4M3 exponent field) doubles the result exactly
+    m = n = k = 8192
+    a, sfa, b, sfb = _random_case(m, n, k, 0xB2000300)
+    rng = np.random.default_rng(8192)
+    rows = np.sort(rng.choice(m, size=16, replace=False)).astype(np.int32)
+    cols = np.sort(rng.choice(n, size=256, replace=False)).astype(np.int32)
+    ref = oracle.gemm_sampled(a, b, sfa, sfb, rows, cols)
+    da, db, dsfa, dsfb = _dev(a), _dev(b), _dev(sfa), _dev(sfb)
+    out = ops.gemm(da, db, dsfa, dsfb)
+    check_gemm_parity(out.cpu().numpy()[np.ix_(rows, cols)], ref)
+    sfa2 = np.where((sfa >= 8) & (sfa < 0x70), sfa + 8, sfa).astype(np.uint8)
+    doubled_everywhere = bool(((sfa == 0) | ((sfa >= 8) & (sfa < 0x70))).all())
+    out2 = ops.gemm(da, db, _dev(sfa2), dsfb)
+    if doubled_everywhere:
+        sel = torch.isfinite(out2) & (out.abs() >= 2.0 ** -13)
+        assert torch.equal(out2[sel], (out * 2)[sel])
+    _no_device_error()
+
+
+def test_fp32_and_batched_entry_points(ops):
+    from sm120_nvfp4_b200 import _lib
+    L = _lib.lib()
+    groups, m, n, k = 3, 130, 264, 320
+    As, Bs, SAs, SBs, refs = [], [], [], [], []
+    for g in range(groups):
+        a, sfa, b, sfb = _random_case(m, n, k, 500 + 10 * g)
+        As.append(a); Bs.append(b); SAs.append(sfa); SBs.append(sfb)
+        refs.append(oracle.gemm(a, b, sfa, sfb)[0])
+    a, b = _dev(np.stack(As)), _dev(np.stack(Bs))
+    sfa, sfb = _dev(np.stack(SAs)), _dev(np.stack(SBs))
+    stream = torch.cuda.current_stream().cuda_stream
+    for tile_n in (0, 64, 256):
+        L.b200_nvfp4_set_tile_n(tile_n)
+        c16 = torch.full((groups, m, n), float("nan"), dtype=torch.float16, device="cuda")
+        c32 = torch.full((groups, m, n), float("nan"), dtype=torch.float32, device="cuda")
+        assert L.b200_nvfp4_gemm(groups, m, n, k, a.data_ptr(), b.data_ptr(), sfa.data_ptr(),
+                                 sfb.data_ptr(), c16.data_ptr(), 0, stream) == 0
+        assert L.b200_nvfp4_gemm(groups, m, n, k, a.data_ptr(), b.data_ptr(), sfa.data_ptr(),
+                                 sfb.data_ptr(), c32.data_ptr(), 1, stream) == 0
+        torch.cuda.synchronize()
+        for g in range(groups):
+            check_gemm_parity(c16[g].cpu().numpy(), refs[g])
+            got32 = c32[g].cpu().numpy()
+            rel = np.abs(got32 - refs[g]).max() / np.abs(refs[g]).max()
+            assert rel < 1e-5, rel
+    L.b200_nvfp4_set_tile_n(0)
+    _no_device_error()
+
+
+def test_splitk_entry_point_and_workspace_contract(ops):
+    from sm120_nvfp4_b200 import _lib
+    L = _lib.lib()
+    m, n, k = 128, 384, 2048
+    a, sfa, b, sfb = _random_case(m, n, k, 900)
+    ref32, _ = oracle.gemm(a, b, sfa, sfb)
+    da, db, dsfa, dsfb = _dev(a), _dev(b), _dev(sfa), _dev(sfb)
+    out = torch.empty((m, n), dtype=torch.float16, device="cuda")
+    ws_bytes = L.b200_nvfp4_gemm_workspace_bytes(m, n, k)
+    assert ws_bytes == 4 * m * n * 4
+    ws = torch.zeros(ws_bytes // 4, dtype=torch.float32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    assert L.b200_nvfp4_gemm_auto(m, n, k, da.data_ptr(), db.data_ptr(), dsfa.data_ptr(), dsfb.data_ptr(),
+                                  out.data_ptr(), ws.data_ptr(), ws_bytes - 4, stream) == 3
+    assert L.b200_nvfp4_gemm_auto(m, n, k, da.data_ptr(), db.data_ptr(), dsfa.data_ptr(), dsfb.data_ptr(),
+                                  out.data_ptr(), ws.data_ptr(), ws_bytes, stream) == 0
+    torch.cuda.synchronize()
+    check_gemm_parity(out.cpu().numpy(), ref32)
+    # the workspace holds the four FP32 partial slices; the output is their sum in split order
+    partial = ws.view(4, m, n).cpu().numpy()
+    np.testing.assert_array_equal(oracle.splitk_reduce(partial), out.cpu().numpy())
+    _no_device_error()
