@@ -185,11 +185,18 @@ B200_NVFP4_API int b200_nvfp4_expert_moe(void* output, const void* input, const 
  * was recorded. No counterpart in the reference. */
 B200_NVFP4_API int b200_nvfp4_device_error(int* code);
 
-/* Forces the tile width (output columns per CTA tile: 32, 64, 128 or 256) of every GEMM
- * launched afterwards by this process; 0 restores the built-in choice. For tests and
+/* Forces the tile shape of every GEMM launched afterwards by this process: 64, 128 or 256 =
+ * a 128-row tile of that many columns on one CTA; 512 = the 256 x 256 tile on a CTA pair
+ * (FP16 output only; FP32 output falls back to 256); 0 restores the built-in choice. For tests and
  * tuning. No counterpart in the reference. Returns B200_NVFP4_INVALID_ARGUMENT for any other
  * value. */
 B200_NVFP4_API int b200_nvfp4_set_tile_n(int tile_n);
+
+/* Debug aid: copies the first `count` (<= 2048) 64-bit time stamps the GEMM kernel recorded
+ * when the environment variable B200_NVFP4_DEBUG has bit 64 set (first two CTAs, first 64
+ * pipeline iterations; layout ((cta*4 + role)*64 + iter)*2 + {before, after}; SM clock
+ * cycles). SYNCHRONISES. No counterpart in the reference. */
+B200_NVFP4_API int b200_nvfp4_debug_trace(unsigned long long* out, int count);
 
 /* Number of kernel launches this library has issued from the calling process since load
  * (for launch accounting in benchmarks). No counterpart in the reference. */

@@ -1,6 +1,8 @@
 // Host launchers and C ABI of the dense / batched / split-K / grouped NVFP4 GEMM.
 #include <atomic>
 #include <cstdint>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -13,6 +15,7 @@
 namespace b200 {
 
 __device__ int g_device_error = 0;
+__device__ unsigned long long g_trace[2048];
 
 int* device_error_word() {
   constexpr int kMaxDevices = 64;
@@ -61,15 +64,15 @@ struct LaunchSpec {
   bool exact_m_tiles;      // expected_m_tiles is exact (dense) rather than a hint (grouped)
 };
 
-template <int BN, bool F32>
+template <int BN, bool F32, bool kTwoCta>
 int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t stream) {
-  using Cfg = GemmCfg<BN>;
-  auto kernel = nvfp4_gemm_kernel<BN, F32>;
+  using Cfg = GemmCfg<BN, kTwoCta>;
+  auto kernel = nvfp4_gemm_kernel<BN, F32, kTwoCta>;
   static std::once_flag once[64];
   static cudaError_t attr_status[64];
   std::call_once(once[dev.device], [&] {
     attr_status[dev.device] = cudaFuncSetAttribute(
-        kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
   });
   if (attr_status[dev.device] != cudaSuccess) return B200_NVFP4_CUDA_ERROR;
 
@@ -77,8 +80,8 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   const uint64_t row_bytes = static_cast<uint64_t>(s.k) / 2;
   if (!encode_tmap_2d_u8(&tmap_a, s.a, static_cast<uint64_t>(s.a_rows_total), row_bytes, kBlockM,
                          kStageKBytes, CU_TENSOR_MAP_SWIZZLE_128B) ||
-      !encode_tmap_2d_u8(&tmap_b, s.b, static_cast<uint64_t>(s.b_rows_total), row_bytes, BN,
-                         kStageKBytes, CU_TENSOR_MAP_SWIZZLE_128B)) {
+      !encode_tmap_2d_u8(&tmap_b, s.b, static_cast<uint64_t>(s.b_rows_total), row_bytes,
+                         Cfg::kBRows, kStageKBytes, CU_TENSOR_MAP_SWIZZLE_128B)) {
     return B200_NVFP4_CUDA_ERROR;
   }
 
@@ -98,52 +101,101 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   p.out_split_stride = s.out_split_stride;
   p.group_alpha = s.group_alpha;
   p.num_splits = s.num_splits;
-  p.raster_m = 16;
+  p.raster_m = kTwoCta ? 8 : 16;
   p.tiles_out = s.tiles_out;
   p.cu_tiles_out = s.cu_tiles_out;
   p.error = device_error_word();
+  p.num_stages = Cfg::stages_for(s.num_groups);
+  { const char* e = std::getenv("B200_NVFP4_DEBUG"); p.debug = e ? std::atoi(e) : 0; }
+  p.trace = nullptr;
+  if (p.debug & 64) { void* tp = nullptr; if (cudaGetSymbolAddress(&tp, g_trace) == cudaSuccess) p.trace = static_cast<unsigned long long*>(tp); }
 
+  // One persistent worker (a CTA, or a pair of CTAs) per SM (or per SM pair).
   const int n_tiles = (s.n + BN - 1) / BN;
-  long long tasks = static_cast<long long>(s.expected_m_tiles) * n_tiles * s.num_splits;
-  int grid = dev.sm_count;
-  if (s.exact_m_tiles && tasks < grid) grid = static_cast<int>(tasks);
-  if (grid < 1) grid = 1;
-  kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmap_a, tmap_b, p);
+  const long long m_tiles = kTwoCta ? (s.expected_m_tiles + 1) / 2 : s.expected_m_tiles;
+  long long tasks = m_tiles * n_tiles * s.num_splits;
+  int workers = dev.sm_count / Cfg::kCtas;
+  if (kTwoCta) {
+    // Not every SM need be pairable: ask how many pairs can be resident at once, so the
+    // persistent grid never queues a pair behind a running one.
+    static std::once_flag pair_once[64];
+    static int max_pairs[64];
+    std::call_once(pair_once[dev.device], [&] {
+      cudaLaunchConfig_t probe = {};
+      probe.gridDim = dim3(static_cast<unsigned>(dev.sm_count));
+      probe.blockDim = dim3(kGemmThreads);
+      probe.dynamicSmemBytes = kSmemBudget;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      probe.attrs = attr;
+      probe.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &probe) != cudaSuccess || n < 1) n = dev.sm_count / 2;
+      max_pairs[dev.device] = n;
+    });
+    if (p.debug & 16) fprintf(stderr, "max active pairs = %d (sm_count %d)\n", max_pairs[dev.device], dev.sm_count);
+    if (!(p.debug & 32) && workers > max_pairs[dev.device]) workers = max_pairs[dev.device];
+  }
+  if (s.exact_m_tiles && tasks < workers) workers = static_cast<int>(tasks);
+  if (workers < 1) workers = 1;
+
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(static_cast<unsigned>(workers * Cfg::kCtas));
+  config.blockDim = dim3(kGemmThreads);
+  config.dynamicSmemBytes = Cfg::smem_bytes(s.num_groups);
+  config.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = Cfg::kCtas;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  config.attrs = attrs;
+  config.numAttrs = 1;
+  const cudaError_t launched = cudaLaunchKernelEx(&config, kernel, tmap_a, tmap_b, p);
   count_launch();
-  return cudaPeekAtLastError() == cudaSuccess ? B200_NVFP4_SUCCESS : B200_NVFP4_CUDA_ERROR;
+  return launched == cudaSuccess && cudaPeekAtLastError() == cudaSuccess ? B200_NVFP4_SUCCESS
+                                                                          : B200_NVFP4_CUDA_ERROR;
 }
 
-// Tile width: 256 columns once there is at least a wave of such tiles (tensor-bound
-// shapes); otherwise the widest tile that still gives every SM a task, because skinny
-// problems are bound by streaming B from HBM and need all SMs pulling.
-int pick_tile_n(const LaunchSpec& s, const DeviceInfo& dev) {
+// Tile shape. expected_m_tiles counts 128-row tiles.
+//   256 x 256 on a CTA pair once there is about a wave of such tiles: tensor-bound shapes,
+//     where halving the B traffic per CTA and the deeper pipeline pay;
+//   128 x 256 / 128 x 128 / 128 x 64 on single CTAs otherwise - the widest tile that still
+//     gives most SMs a task, because skinny problems are bound by streaming B from HBM and
+//     need every SM pulling.
+// The override (b200_nvfp4_set_tile_n) takes 64 / 128 / 256 for single-CTA tiles and 512 for
+// the CTA-pair tile.
+int pick_tile(const LaunchSpec& s, const DeviceInfo& dev) {
   const long long mt = s.expected_m_tiles > 0 ? s.expected_m_tiles : 1;
   const long long splits = s.num_splits;
   auto tasks = [&](int bn) { return mt * ((s.n + bn - 1) / bn) * splits; };
+  if (!s.out_f32 && splits == 1 && ((mt + 1) / 2) * ((s.n + 255) / 256) >= dev.sm_count / 2) return 512;
   if (tasks(256) >= dev.sm_count) return 256;
   if (tasks(128) >= dev.sm_count * 3 / 4) return 128;
-  if (tasks(64) >= dev.sm_count * 3 / 4 || s.n <= 64) return s.n <= 32 ? 32 : 64;
-  return 32;
+  return 64;
 }
 
-int launch_gemm(const LaunchSpec& s, cudaStream_t stream, int force_tile_n = 0) {
+int launch_gemm(const LaunchSpec& s, cudaStream_t stream, int force_tile = 0) {
   const DeviceInfo& dev = current_device_info();
   if (!dev.ok) return B200_NVFP4_CUDA_ERROR;
   if (!device_supported(dev)) return B200_NVFP4_UNSUPPORTED_DEVICE;
-  const int bn = force_tile_n ? force_tile_n : pick_tile_n(s, dev);
-  switch (bn) {
+  int tile = force_tile ? force_tile : pick_tile(s, dev);
+  if (tile == 512 && s.out_f32) tile = 256;
+  switch (tile) {
+    case 512:
+      return launch_instance<256, false, true>(s, dev, stream);
     case 256:
-      return s.out_f32 ? launch_instance<256, true>(s, dev, stream)
-                       : launch_instance<256, false>(s, dev, stream);
+      return s.out_f32 ? launch_instance<256, true, false>(s, dev, stream)
+                       : launch_instance<256, false, false>(s, dev, stream);
     case 128:
-      return s.out_f32 ? launch_instance<128, true>(s, dev, stream)
-                       : launch_instance<128, false>(s, dev, stream);
+      return s.out_f32 ? launch_instance<128, true, false>(s, dev, stream)
+                       : launch_instance<128, false, false>(s, dev, stream);
     case 64:
-      return s.out_f32 ? launch_instance<64, true>(s, dev, stream)
-                       : launch_instance<64, false>(s, dev, stream);
-    case 32:
-      return s.out_f32 ? launch_instance<32, true>(s, dev, stream)
-                       : launch_instance<32, false>(s, dev, stream);
+      return s.out_f32 ? launch_instance<64, true, false>(s, dev, stream)
+                       : launch_instance<64, false, false>(s, dev, stream);
     default:
       return B200_NVFP4_INVALID_ARGUMENT;
   }
@@ -410,10 +462,15 @@ int b200_nvfp4_device_error(int* code) {
 }
 
 int b200_nvfp4_set_tile_n(int tile_n) {
-  if (tile_n != 0 && tile_n != 32 && tile_n != 64 && tile_n != 128 && tile_n != 256)
+  if (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 256 && tile_n != 512)
     return B200_NVFP4_INVALID_ARGUMENT;
   b200::g_tile_n_override.store(tile_n, std::memory_order_relaxed);
   return B200_NVFP4_SUCCESS;
+}
+
+int b200_nvfp4_debug_trace(unsigned long long* out, int count) {
+  if (out == nullptr || count <= 0 || count > 2048) return B200_NVFP4_INVALID_ARGUMENT;
+  return cudaMemcpyFromSymbol(out, b200::g_trace, sizeof(unsigned long long) * count) == cudaSuccess ? B200_NVFP4_SUCCESS : B200_NVFP4_CUDA_ERROR;
 }
 
 long long b200_nvfp4_launch_count(void) {

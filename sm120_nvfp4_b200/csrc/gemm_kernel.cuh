@@ -14,15 +14,26 @@
 // (src/gemm/specialized/m128_gemm.cu:43-365), group_gemm_nvfp4_kernel and its four
 // set-up kernels (src/grouped_gemm/kernels.cuh:66-449).
 //
-// Structure of one CTA (192 threads, one CTA per SM):
-//   warp 0      producer: TMA loads of the A / B tiles (128-byte swizzle) and untiled bulk
-//               copies of the scale atoms into a ring of shared-memory stages
-//   warp 1      MMA issuer: tcgen05.cp moves scale atoms shared -> tensor memory, then
-//               tcgen05.mma kind::mxf4nvf4 (128 x BN x 64 per instruction) accumulates FP32
-//               in tensor memory; tcgen05.commit releases the stage / publishes the tile
-//   warps 2-5   epilogue: tcgen05.ld of the accumulator (one 32-lane quarter per warp),
-//               conversion, staging through shared memory, coalesced 16-byte stores with
-//               row / column predicates
+// Two variants of one template:
+//   one CTA per tile   128 x BN output tile, tcgen05 cta_group::1, BN = 64 / 128 / 256
+//   CTA pair per tile  256 x 256 output tile computed by two CTAs of a cluster with
+//                      cta_group::2 MMAs: each CTA loads its 128 rows of A and its half of
+//                      B, so a pair moves 1.5x fewer operand bytes per flop than two single
+//                      CTAs and fits a deeper pipeline. No multicast load is used anywhere.
+//
+// Structure of one CTA (512 threads, one CTA per SM):
+//   warps 0, 2  loaders: TMA loads of the A tile / the B tile (128-byte swizzle) into a ring
+//               of shared-memory stages
+//   warp 3      scale loader: untiled bulk copies of the stage's scale atoms
+//   warps 4-7   scale movers, one per TMEM lane quarter: read the landed atoms from shared
+//               memory and write them into the stage's tensor-memory buffer with tcgen05.st
+//               (two wide stores per stage instead of a dozen tcgen05.cp, whose issue cost
+//               would exceed the MMA time of a stage), ahead of the MMAs
+//   warp 1      MMA issuer (first CTA of a pair only): tcgen05.mma kind::mxf4nvf4
+//               (M x BN x 64 per instruction) accumulates FP32 in tensor memory;
+//               tcgen05.commit releases the stage / publishes the tile
+//   warps 8-15  epilogue: tcgen05.ld of the accumulator (a 32-lane quarter and half of the
+//               columns per warp), conversion, 16-byte stores with row / column predicates
 // All mbarrier waits are bounded (ptx::mbar_wait); a timeout is reported through
 // GemmParams::error instead of hanging.
 #pragma once
@@ -33,15 +44,25 @@
 
 namespace b200 {
 
-constexpr int kBlockM = 128;        // rows of A per tile = UMMA M
+constexpr int kBlockM = 128;        // rows of A per CTA = rows of one UMMA half
 constexpr int kStageKBytes = 128;   // bytes of K per stage row = one swizzle span
 constexpr int kStageK = 256;        // E2M1 values of K per stage
 constexpr int kAtomBytes = 512;     // one scale atom: 128 rows x 4 k-blocks
 constexpr int kMaxGroups = 1024;
-constexpr int kGemmThreads = 192;
-constexpr int kStagingRowBytes = 144;  // 128 payload bytes + 16 pad: conflict-free 16-byte rows
-constexpr int kStagingBytes = 4 * 32 * kStagingRowBytes;
-constexpr int kSmemBudget = 232448;  // 227 KB opt-in limit per CTA
+constexpr int kEpilogueWarps = 8;       // two per TMEM lane quarter, each takes half the columns
+// Warp roles. Every asynchronous-copy instruction costs the issuing thread tens of
+// nanoseconds, and a k-stage of FP4 MMAs lasts only ~0.3 us, so the A tile, the B tile and
+// the scale atoms are each issued by a thread of their own warp.
+constexpr int kWarpLoadA = 0;
+constexpr int kWarpMma = 1;
+constexpr int kWarpLoadB = 2;
+constexpr int kWarpLoadSf = 3;
+constexpr int kFirstSfMoverWarp = 4;    // four warps, one per TMEM lane quarter
+constexpr int kFirstEpilogueWarp = 8;
+constexpr int kGemmThreads = 32 * (kFirstEpilogueWarp + kEpilogueWarps);
+constexpr int kMaxStages = 8;
+constexpr int kBarrierBytes = 384;      // 4 x kMaxStages + 4 mbarriers, TMEM base, abort flag
+constexpr int kSmemBudget = 232448;     // 227 KB opt-in limit per CTA
 
 struct GemmParams {
   int num_groups;
@@ -63,29 +84,50 @@ struct GemmParams {
   int* tiles_out;             // optional [G]   ceil(rows/128) per group
   int* cu_tiles_out;          // optional [G+1] exclusive prefix of tiles_out
   int* error;                 // device word that receives a non-zero code on a timed-out wait
+  int num_stages;             // depth of the shared-memory ring (host-computed, <= kMaxStages)
+  int debug;                  // experiment switches (0 in production)
+  unsigned long long* trace;  // optional time-stamp buffer (debug bit 64), else nullptr
 };
 
-template <int BN>
+template <int BN, bool kTwoCta>
 struct GemmCfg {
-  static_assert(BN == 32 || BN == 64 || BN == 128 || BN == 256, "unsupported tile width");
+  // Tiles narrower than 128 columns select their part of a 128-row scale atom by offsetting
+  // the TMEM address of the scale columns; the hardware wants that address two-column
+  // aligned, which rules out 32-wide tiles (they would need odd offsets).
+  static_assert(BN == 64 || BN == 128 || BN == 256, "unsupported tile width");
+  static_assert(!kTwoCta || BN == 256, "the CTA-pair variant is built for 256-wide tiles");
+  static constexpr int kCtas = kTwoCta ? 2 : 1;
+  static constexpr int kTileM = kBlockM * kCtas;            // rows of one output tile
+  static constexpr int kBRows = BN / kCtas;                 // rows of B this CTA loads
   static constexpr int kSfbGroups = (BN + 127) / 128;       // 128-row scale tiles per B tile
   static constexpr int kSfbColsPerMma = 4 * kSfbGroups;     // TMEM columns of SFB per MMA
   static constexpr int kAccStages = BN <= 128 ? 2 : 1;
-  static constexpr int kSfaCol = kAccStages * BN;
-  static constexpr int kSfbCol = kSfaCol + 16;
-  static constexpr int kUsedCols = kSfbCol + 4 * kSfbColsPerMma;
-  static constexpr int kTmemCols = kUsedCols <= 128 ? 128 : (kUsedCols <= 256 ? 256 : 512);
+  // Tensor memory: accumulator stage(s) first, then one scale-factor buffer per shared-memory
+  // stage, so the scale copies of a k-stage can be issued (by their own warp) while the MMAs
+  // of earlier stages are still running.
+  static constexpr int kSfColsPerBuf = 16 + 4 * kSfbColsPerMma;   // 4 MMAs: SFA 4x4, SFB 4xN/32
+  static constexpr int kSfBase = kAccStages * BN;
+  static constexpr int kMaxSfBufs = (512 - kSfBase) / kSfColsPerBuf;
+  static constexpr int kTmemCols = 512;
   static constexpr int kABytes = kBlockM * kStageKBytes;
-  static constexpr int kBBytes = BN * kStageKBytes;
+  static constexpr int kBBytes = kBRows * kStageKBytes;
   static constexpr int kSfaBytes = 4 * kAtomBytes;
   static constexpr int kSfbBytes = kSfbGroups * 4 * kAtomBytes;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kFixedBytes = 1024 /*alignment slack*/ + kStagingBytes + 256 /*barriers*/ +
-                                     3 * (kMaxGroups + 1) * 4;
-  static constexpr int kStagesRaw = (kSmemBudget - kFixedBytes) / kStageBytes;
-  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kSmemBytes = kFixedBytes + kStages * kStageBytes;
-  static_assert(kStages >= 3, "pipeline too shallow");
+
+  // Shared memory: [stages][barriers][group tables]; +1024 slack to align the base.
+  static constexpr int fixed_bytes(int num_groups) {
+    return 1024 + kBarrierBytes + 3 * (num_groups + 1) * 4;
+  }
+  static constexpr int stages_for(int num_groups) {
+    int s = (kSmemBudget - fixed_bytes(num_groups)) / kStageBytes;
+    s = s > kMaxStages ? kMaxStages : s;
+    return s > kMaxSfBufs ? kMaxSfBufs : s;
+  }
+  static constexpr int smem_bytes(int num_groups) {
+    return fixed_bytes(num_groups) + stages_for(num_groups) * kStageBytes;
+  }
+  static_assert(stages_for(kMaxGroups) >= 3, "pipeline too shallow");
 };
 
 struct TileCoord {
@@ -118,37 +160,62 @@ __device__ __forceinline__ TileCoord decode_tile(int task, int total_mt, int n_t
   return t;
 }
 
+// Debug time stamps: trace[((cta * 4 + role) * 64 + iter) * 2 + which] = SM clock counter.
+__device__ __forceinline__ void trace_stamp(const GemmParams& p, int role, int iter, int which) {
+  if ((p.debug & 64) && p.trace != nullptr && blockIdx.x < 2 && iter < 64) {
+    const unsigned long long t = static_cast<unsigned long long>(clock64());
+    p.trace[((blockIdx.x * 4 + role) * 64 + iter) * 2 + which] = t;
+  }
+}
+
+// Fine-grained stamps of the MMA issuer: trace[1024 + iter * 16 + k].
+__device__ __forceinline__ void trace_fine(const GemmParams& p, int iter, int k) {
+  if ((p.debug & 256) && p.trace != nullptr && blockIdx.x == 0 && iter < 60)
+    p.trace[1024 + iter * 16 + k] = static_cast<unsigned long long>(clock64());
+}
+
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <int BN, bool kOutF32>
+template <int BN, bool kOutF32, bool kTwoCta>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
-  using Cfg = GemmCfg<BN>;
-  constexpr int kStages = Cfg::kStages;
+  using Cfg = GemmCfg<BN, kTwoCta>;
+  constexpr int kCtas = Cfg::kCtas;
   constexpr int kAccStages = Cfg::kAccStages;
+  constexpr int kTileM = Cfg::kTileM;
+  const int kStages = p.num_stages;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* stage_base = smem;
-  uint8_t* staging = smem + kStages * Cfg::kStageBytes;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + kStagingBytes);
-  uint64_t* empty_bar = full_bar + kStages;
-  uint64_t* acc_full_bar = empty_bar + kStages;
-  uint64_t* acc_empty_bar = acc_full_bar + kAccStages;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty_bar + kAccStages);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+  // full:      A / B tiles of the stage landed (pair: in both CTAs; lives in the first CTA)
+  // empty:     the MMAs that read the stage are done
+  // sf_landed: the stage's scale atoms landed in this CTA's shared memory
+  // sf_full:   the stage's scales are in tensor memory (pair: of both CTAs; first CTA's)
+  uint64_t* empty_bar = full_bar + kMaxStages;
+  uint64_t* sf_landed_bar = empty_bar + kMaxStages;
+  uint64_t* sf_full_bar = sf_landed_bar + kMaxStages;
+  uint64_t* acc_full_bar = sf_full_bar + kMaxStages;
+  uint64_t* acc_empty_bar = acc_full_bar + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
   int* abort_flag = reinterpret_cast<int*>(tmem_holder + 1);
-  int* s_cu_tiles = reinterpret_cast<int*>(staging + kStagingBytes + 256);
+  int* s_cu_tiles = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(full_bar) + kBarrierBytes);
   int* s_row0 = s_cu_tiles + (p.num_groups + 1);
   int* s_rows = s_row0 + (p.num_groups + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int G = p.num_groups;
+  const uint32_t cta_rank = kTwoCta ? ptx::cluster_cta_rank() : 0u;
+  const bool leader = cta_rank == 0;
+  const int worker = static_cast<int>(blockIdx.x) / kCtas;     // CTA or CTA pair
+  const int num_workers = static_cast<int>(gridDim.x) / kCtas;
 
   // ---- group tables: valid rows, first row and m-tile prefix of every group
   for (int g = threadIdx.x; g < G; g += kGemmThreads) {
@@ -156,24 +223,26 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     rows = rows > 0 ? rows : 0;
     s_rows[g] = rows;
     s_row0[g] = p.cu_seqlens ? p.cu_seqlens[g] : g * p.m_uniform;
-    s_cu_tiles[g] = (rows + kBlockM - 1) / kBlockM;
+    s_cu_tiles[g] = (rows + kTileM - 1) / kTileM;
   }
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
-      ptx::mbar_init(full_bar + s, 1);
+      ptx::mbar_init(full_bar + s, 2);  // the A loader and the B loader of the owning CTA
       ptx::mbar_init(empty_bar + s, 1);
+      ptx::mbar_init(sf_landed_bar + s, 1);
+      ptx::mbar_init(sf_full_bar + s, 4 * kCtas);  // one arrival per mover warp
     }
-    for (int s = 0; s < kAccStages; ++s) {
+    for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(acc_full_bar + s, 1);
-      ptx::mbar_init(acc_empty_bar + s, 4);
+      ptx::mbar_init(acc_empty_bar + s, kEpilogueWarps * kCtas);
     }
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
   }
   __syncthreads();
-  if (warp == 0) {  // exclusive scan of the per-group tile counts, 32 groups at a time
+  if (warp == kWarpLoadA) {  // exclusive scan of the per-group tile counts, 32 groups at a time
     int carry = 0;
     for (int base = 0; base < G; base += 32) {
       int v = (base + lane < G) ? s_cu_tiles[base + lane] : 0;
@@ -183,23 +252,36 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         int o = __shfl_up_sync(0xffffffffu, incl, d);
         if (lane >= d) incl += o;
       }
-      if (base + lane < G) {
-        if (blockIdx.x == 0 && p.tiles_out) p.tiles_out[base + lane] = v;
-        if (blockIdx.x == 0 && p.cu_tiles_out) p.cu_tiles_out[base + lane] = carry + incl - v;
-        s_cu_tiles[base + lane] = carry + incl - v;
-      }
+      if (base + lane < G) s_cu_tiles[base + lane] = carry + incl - v;
       carry += __shfl_sync(0xffffffffu, incl, 31);
     }
-    if (lane == 0) {
-      s_cu_tiles[G] = carry;
-      if (blockIdx.x == 0 && p.cu_tiles_out) p.cu_tiles_out[G] = carry;
+    if (lane == 0) s_cu_tiles[G] = carry;
+    if (blockIdx.x == 0 && (p.tiles_out || p.cu_tiles_out)) {
+      // the reference ABI's scratch outputs: 128-row tile count per group and its prefix
+      int run = 0;
+      for (int base = 0; base < G; base += 32) {
+        int v = (base + lane < G) ? (s_rows[base + lane] + kBlockM - 1) / kBlockM : 0;
+        int incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          int o = __shfl_up_sync(0xffffffffu, incl, d);
+          if (lane >= d) incl += o;
+        }
+        if (base + lane < G) {
+          if (p.tiles_out) p.tiles_out[base + lane] = v;
+          if (p.cu_tiles_out) p.cu_tiles_out[base + lane] = run + incl - v;
+        }
+        run += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0 && p.cu_tiles_out) p.cu_tiles_out[G] = run;
     }
-  } else if (warp == 1) {
-    ptx::tmem_alloc(tmem_holder, Cfg::kTmemCols);
-    ptx::tmem_relinquish();
+  } else if (warp == kWarpMma) {
+    ptx::tmem_alloc<kCtas>(tmem_holder, Cfg::kTmemCols);
+    ptx::tmem_relinquish<kCtas>();
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if constexpr (kTwoCta) ptx::cluster_sync();  // the partner's barriers are initialised too
   ptx::tc_fence_after_sync();
 
   const uint32_t tmem_base = *tmem_holder;
@@ -210,18 +292,54 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int k_stages = (kt + 3) / 4;            // pipeline stages along K
   const int n_sf_tiles = (p.n + 127) / 128;     // 128-row scale tiles of B
 
-  if (warp == 0) {
-    // =============================== producer ===============================
+  if (warp == kWarpLoadA || warp == kWarpLoadB) {
+    // ============================ operand loaders ============================
+    // One thread per operand. Completion bytes are counted on the barrier of the first CTA
+    // (in a pair both CTAs' loads report there, and only the first CTA's loader arms it, for
+    // both halves), so the MMA issuer waits on one barrier per stage.
+    if (lane == 0) {
+      const bool is_a = warp == kWarpLoadA;
+      const CUtensorMap* tmap = is_a ? &tmap_a : &tmap_b;
+      const uint32_t bytes = is_a ? Cfg::kABytes : Cfg::kBBytes;
+      int stage = 0, iter = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int task = worker; task < total_tasks && ok; task += num_workers) {
+        TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
+        const int row = is_a ? s_row0[t.g] + t.mt * kTileM + static_cast<int>(cta_rank) * kBlockM
+                             : t.g * p.b_group_rows + t.nt * BN + static_cast<int>(cta_rank) * Cfg::kBRows;
+        const int ks_begin = (k_stages * t.split) / p.num_splits;
+        const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
+        for (int ks = ks_begin; ks < ks_end; ++ks) {
+          if (is_a) trace_stamp(p, 0, iter, 0);
+          if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, 1)) { ok = false; break; }
+          if (is_a) trace_stamp(p, 0, iter++, 1);
+          uint8_t* dst = stage_base + stage * Cfg::kStageBytes + (is_a ? 0 : Cfg::kABytes);
+          if constexpr (kTwoCta) {
+            if (leader) ptx::mbar_arrive_expect_tx(full_bar + stage, 2 * bytes);
+            ptx::tma_load_2d_pair(dst, tmap, ptx::map_to_cta(full_bar + stage, 0), ks * kStageKBytes, row);
+          } else {
+            ptx::mbar_arrive_expect_tx(full_bar + stage, bytes);
+            ptx::tma_load_2d(dst, tmap, full_bar + stage, ks * kStageKBytes, row);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == kWarpLoadSf) {
+    // ============================== scale loader =============================
+    // The scale atoms are small and sit on a barrier of their own, so their trip into
+    // tensor memory overlaps the (longer) flight of the operand tiles.
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int task = blockIdx.x; task < total_tasks && ok; task += gridDim.x) {
+      for (int task = worker; task < total_tasks && ok; task += num_workers) {
         TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
-        const int a_row = s_row0[t.g] + t.mt * kBlockM;
-        const int b_row = t.g * p.b_group_rows + t.nt * BN;
-        const uint8_t* sfa_tile = p.sfa + t.g * p.sfa_group_stride +
-                                  static_cast<long long>(t.mt) * kt * kAtomBytes;
+        const uint8_t* sfa_tile =
+            p.sfa + t.g * p.sfa_group_stride +
+            static_cast<long long>(t.mt * kCtas + static_cast<int>(cta_rank)) * kt * kAtomBytes;
         const int sf_tile0 = (t.nt * BN) / 128;
         const uint8_t* sfb_tile = p.sfb + t.g * p.sfb_group_stride +
                                   static_cast<long long>(sf_tile0) * kt * kAtomBytes;
@@ -230,36 +348,32 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int ks_begin = (k_stages * t.split) / p.num_splits;
         const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
         for (int ks = ks_begin; ks < ks_end; ++ks) {
-          if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, 1)) { ok = false; break; }
-          uint8_t* sa = stage_base + stage * Cfg::kStageBytes;
-          uint8_t* sb = sa + Cfg::kABytes;
-          uint8_t* ssfa = sb + Cfg::kBBytes;
+          if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, 8)) { ok = false; break; }
+          uint8_t* ssfa = stage_base + stage * Cfg::kStageBytes + Cfg::kABytes + Cfg::kBBytes;
           uint8_t* ssfb = ssfa + Cfg::kSfaBytes;
           const int atoms = min(4, kt - ks * 4);
           const uint32_t sf_bytes = static_cast<uint32_t>(atoms) * kAtomBytes;
-          ptx::mbar_arrive_expect_tx(full_bar + stage,
-                                     Cfg::kABytes + Cfg::kBBytes + sf_bytes * (1 + sfb_groups));
-          ptx::tma_load_2d(sa, &tmap_a, full_bar + stage, ks * kStageKBytes, a_row);
-          ptx::tma_load_2d(sb, &tmap_b, full_bar + stage, ks * kStageKBytes, b_row);
+          ptx::mbar_arrive_expect_tx(sf_landed_bar + stage, sf_bytes * (1 + sfb_groups));
           ptx::bulk_load(ssfa, sfa_tile + static_cast<long long>(ks) * 4 * kAtomBytes, sf_bytes,
-                         full_bar + stage);
+                         sf_landed_bar + stage);
           for (int gi = 0; gi < sfb_groups; ++gi)
             ptx::bulk_load(ssfb + gi * 4 * kAtomBytes,
                            sfb_tile + (static_cast<long long>(gi) * kt + ks * 4) * kAtomBytes,
-                           sf_bytes, full_bar + stage);
+                           sf_bytes, sf_landed_bar + stage);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
+  } else if (warp == kWarpMma) {
     // =============================== MMA issuer ==============================
-    if (lane == 0) {
-      constexpr uint32_t idesc = ptx::make_idesc_nvfp4(kBlockM, BN);
-      int stage = 0, acc = 0;
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = ptx::make_idesc_nvfp4(kTileM, BN);
+      constexpr uint16_t kAllCtas = kTwoCta ? 3 : 1;
+      int stage = 0, acc = 0, iter = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      for (int task = blockIdx.x; task < total_tasks && ok; task += gridDim.x) {
+      for (int task = worker; task < total_tasks && ok; task += num_workers) {
         TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
         const int ks_begin = (k_stages * t.split) / p.num_splits;
         const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
@@ -270,103 +384,157 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         ptx::tc_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int ks = ks_begin; ks < ks_end; ++ks) {
-          if (!ptx::mbar_wait(full_bar + stage, phase, abort_flag, 3)) { ok = false; break; }
+          trace_stamp(p, 1, iter, 0);
+          trace_fine(p, iter, 0);
+          if (!ptx::mbar_wait(sf_full_bar + stage, phase, abort_flag, 3)) { ok = false; break; }
+          trace_stamp(p, 3, iter, 0);
+          trace_fine(p, iter, 1);
+          if (!ptx::mbar_wait(full_bar + stage, phase, abort_flag, 7)) { ok = false; break; }
+          trace_stamp(p, 1, iter, 1);
+          trace_fine(p, iter, 2);
           ptx::tc_fence_after_sync();
-          uint8_t* sa = stage_base + stage * Cfg::kStageBytes;
-          const uint32_t a_addr = ptx::smem_u32(sa);
+          trace_fine(p, iter, 3);
+          const uint32_t a_addr = ptx::smem_u32(stage_base + stage * Cfg::kStageBytes);
           const uint32_t b_addr = a_addr + Cfg::kABytes;
-          const uint32_t sfa_addr = b_addr + Cfg::kBBytes;
-          const uint32_t sfb_addr = sfa_addr + Cfg::kSfaBytes;
           const int atoms = min(4, kt - ks * 4);
-          for (int j = 0; j < atoms; ++j) {
-            ptx::tc_cp_32x128b_warpx4(tmem_base + Cfg::kSfaCol + 4 * j,
-                                      ptx::make_sf_desc(sfa_addr + j * kAtomBytes));
-#pragma unroll
-            for (int gi = 0; gi < Cfg::kSfbGroups; ++gi)
-              ptx::tc_cp_32x128b_warpx4(
-                  tmem_base + Cfg::kSfbCol + j * Cfg::kSfbColsPerMma + 4 * gi,
-                  ptx::make_sf_desc(sfb_addr + (gi * 4 + j) * kAtomBytes));
-          }
+          const uint32_t sfa_col = tmem_base + Cfg::kSfBase + stage * Cfg::kSfColsPerBuf;
+          const uint32_t sfb_col = sfa_col + 16;
           const uint64_t a_desc = ptx::make_kmajor_sw128_desc(a_addr);
           const uint64_t b_desc = ptx::make_kmajor_sw128_desc(b_addr);
+          if ((p.debug & 128) && iter == 1 && p.trace != nullptr && blockIdx.x == 0) {
+            // micro-benchmark: 64 MMAs back to back on this stage, timed to completion
+            const long long t0 = clock64();
+            for (int rep = 0; rep < 16; ++rep)
+              for (int j = 0; j < 4; ++j)
+                ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_desc + 2 * j, b_desc + 2 * j, idesc,
+                                         sfa_col + 4 * j, sfb_col + j * Cfg::kSfbColsPerMma, 1u);
+            const long long t1 = clock64();
+            ptx::tc_commit<kCtas>(acc_full_bar + 1, 1);   // spare barrier (single accumulator stage)
+            ptx::mbar_wait(acc_full_bar + 1, 0, abort_flag, 9);
+            const long long t2 = clock64();
+            p.trace[2040] = static_cast<unsigned long long>(t1 - t0);
+            p.trace[2041] = static_cast<unsigned long long>(t2 - t0);
+          }
+          if (!(p.debug & 2))
           for (int j = 0; j < atoms; ++j) {
             // 64 E2M1 values = 32 bytes along K: +2 in the descriptor's 16-byte address field
-            ptx::tc_mma_nvfp4(tmem_acc, a_desc + 2 * j, b_desc + 2 * j, idesc,
-                              tmem_base + Cfg::kSfaCol + 4 * j,
-                              tmem_base + Cfg::kSfbCol + j * Cfg::kSfbColsPerMma + sfb_sub,
-                              (ks > ks_begin || j > 0) ? 1u : 0u);
+            ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_desc + 2 * j, b_desc + 2 * j, idesc,
+                                     sfa_col + 4 * j, sfb_col + j * Cfg::kSfbColsPerMma + sfb_sub,
+                                     (ks > ks_begin || j > 0) ? 1u : 0u);
+            trace_fine(p, iter, 4 + j);
           }
-          ptx::tc_commit(empty_bar + stage);
+          ptx::tc_commit<kCtas>(empty_bar + stage, kAllCtas);
+          trace_fine(p, iter, 8);
+          trace_stamp(p, 3, iter++, 1);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        ptx::tc_commit(acc_full_bar + acc);
+        ptx::tc_commit<kCtas>(acc_full_bar + acc, kAllCtas);
         if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
       }
     }
     __syncwarp();
-  } else {
-    // ================================ epilogue ===============================
-    const int q = warp & 3;                       // TMEM lane quarter this warp may read
-    uint8_t* my_staging = staging + (warp - 2) * 32 * kStagingRowBytes;
-    constexpr int kChunkCols = kOutF32 ? 32 : (BN < 64 ? BN : 64);   // columns per store pass
-    constexpr int kChunkBytes = kChunkCols * (kOutF32 ? 4 : 2);
-    constexpr int kLanesPerRow = kChunkBytes / 16;
-    constexpr int kRowsPerPass = 32 / kLanesPerRow;
-    constexpr int kElemsPer16B = kOutF32 ? 4 : 8;
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    for (int task = blockIdx.x; task < total_tasks; task += gridDim.x) {
+  } else if (warp >= kFirstSfMoverWarp && warp < kFirstSfMoverWarp + 4) {
+    // ============================== scale movers =============================
+    // Warp q moves the stage's scale atoms from shared memory into lanes 32q..32q+31 of the
+    // stage's tensor-memory buffer (the MMA wants every 32-lane quarter to hold the same 16
+    // bytes per lane: row r of an atom lives in lane r % 32, column r / 32). Lane t reads
+    // the 16 bytes at offset 16 t of each atom. sf_landed[stage] completing also means the
+    // MMAs that last read this buffer are done (the loader refilled the stage only after).
+    const int q = warp & 3;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int task = worker; task < total_tasks && ok; task += num_workers) {
       TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
-      const int rows_valid = s_rows[t.g] - t.mt * kBlockM;
-      const long long out_row0 = static_cast<long long>(s_row0[t.g]) + t.mt * kBlockM;
-      const int col0 = t.nt * BN;
-      // A k-split that owns no k-stage (more splits than stages) contributes zeros: the
-      // accumulator was never written, so its contents are discarded by a zero multiplier.
-      const bool empty_split = (k_stages * t.split) / p.num_splits == (k_stages * (t.split + 1)) / p.num_splits;
-      const float alpha = p.group_alpha ? p.group_alpha[t.g] : 1.0f;
-      if (!ptx::mbar_wait(acc_full_bar + acc, acc_phase, abort_flag, 4)) break;
-      ptx::tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                             static_cast<uint32_t>(acc * BN);
-
-      auto store_chunk = [&](int chunk) {
-        // staging holds 32 rows x kChunkBytes for this warp; write them out row-contiguously
-        __syncwarp();
+      const int ks_begin = (k_stages * t.split) / p.num_splits;
+      const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
+      for (int ks = ks_begin; ks < ks_end; ++ks) {
+        int landed = 1;
+        if (lane == 0) landed = ptx::mbar_wait(sf_landed_bar + stage, phase, abort_flag, 5) ? 1 : 0;
+        landed = __shfl_sync(0xffffffffu, landed, 0);
+        if (!landed) { ok = false; break; }
+        const uint8_t* ssfa = stage_base + stage * Cfg::kStageBytes + Cfg::kABytes + Cfg::kBBytes + lane * 16;
+        const uint8_t* ssfb = ssfa + Cfg::kSfaBytes;
+        const int atoms = min(4, kt - ks * 4);
+        const uint32_t sf_taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                  static_cast<uint32_t>(Cfg::kSfBase + stage * Cfg::kSfColsPerBuf);
+        uint32_t ra[16];
 #pragma unroll
-        for (int pass = 0; pass < 32 / kRowsPerPass; ++pass) {
-          const int r = pass * kRowsPerPass + lane / kLanesPerRow;
-          const int cc = lane % kLanesPerRow;
-          const uint4 v = *reinterpret_cast<const uint4*>(my_staging + r * kStagingRowBytes + cc * 16);
-          const int grow = q * 32 + r;
-          const int col = col0 + chunk * kChunkCols + cc * kElemsPer16B;
-          if (grow < rows_valid && col < p.n) {
-            if constexpr (kOutF32) {
-              float* dst = static_cast<float*>(p.out) + t.split * p.out_split_stride +
-                           (out_row0 + grow) * p.n + col;
-              *reinterpret_cast<uint4*>(dst) = v;
-            } else {
-              __half* dst = static_cast<__half*>(p.out) + t.split * p.out_split_stride +
-                            (out_row0 + grow) * p.n + col;
-              *reinterpret_cast<uint4*>(dst) = v;
-            }
+        for (int j = 0; j < 4; ++j) {
+          uint4 v = make_uint4(0u, 0u, 0u, 0u);
+          if (j < atoms) v = *reinterpret_cast<const uint4*>(ssfa + j * kAtomBytes);
+          ra[4 * j] = v.x; ra[4 * j + 1] = v.y; ra[4 * j + 2] = v.z; ra[4 * j + 3] = v.w;
+        }
+        ptx::tmem_st_32x32b_x16(sf_taddr, ra);
+        uint32_t rb[4 * Cfg::kSfbColsPerMma];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+          for (int gi = 0; gi < Cfg::kSfbGroups; ++gi) {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (j < atoms) v = *reinterpret_cast<const uint4*>(ssfb + (gi * 4 + j) * kAtomBytes);
+            const int c = j * Cfg::kSfbColsPerMma + 4 * gi;
+            rb[c] = v.x; rb[c + 1] = v.y; rb[c + 2] = v.z; rb[c + 3] = v.w;
           }
         }
+        if constexpr (Cfg::kSfbGroups == 2) ptx::tmem_st_32x32b_x32(sf_taddr + 16, rb);
+        else ptx::tmem_st_32x32b_x16(sf_taddr + 16, rb);
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before_sync();
         __syncwarp();
+        if (lane == 0) {
+          if (kTwoCta && !leader) ptx::mbar_arrive_remote(sf_full_bar + stage, 0);
+          else ptx::mbar_arrive(sf_full_bar + stage);
+        }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else {
+    // ================================ epilogue ===============================
+    // Warp w reads TMEM lanes 32*(w%4).. (a hardware rule) and half of the tile's columns.
+    // Each thread owns one output row: after the accumulator is in registers (and handed
+    // back to the MMA warp) it writes its row segment with 16-byte stores.
+    const int q = warp & 3;
+    const int half = (warp - kFirstEpilogueWarp) >> 2;
+    constexpr int kWarpCols = BN / 2;                                 // columns per warp
+    constexpr int kLdCols = 32;                                       // columns per TMEM load
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int task = worker; task < total_tasks; task += num_workers) {
+      TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
+      const int row_in_tile = static_cast<int>(cta_rank) * kBlockM + q * 32 + lane;
+      const bool row_ok = t.mt * kTileM + row_in_tile < s_rows[t.g];
+      const long long out_row = static_cast<long long>(s_row0[t.g]) + t.mt * kTileM + row_in_tile;
+      const int col0 = t.nt * BN + half * kWarpCols;
+      // A k-split that owns no k-stage (more splits than stages) contributes zeros: the
+      // accumulator was never written, so its contents are replaced, not scaled.
+      const bool empty_split = (k_stages * t.split) / p.num_splits == (k_stages * (t.split + 1)) / p.num_splits;
+      const float alpha = p.group_alpha ? p.group_alpha[t.g] : 1.0f;
+      int ready = 1;
+      if (lane == 0) ready = ptx::mbar_wait(acc_full_bar + acc, acc_phase, abort_flag, 4) ? 1 : 0;
+      ready = __shfl_sync(0xffffffffu, ready, 0);
+      if (!ready) break;
+      ptx::tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                             static_cast<uint32_t>(acc * BN + half * kWarpCols);
+      auto release_accumulator = [&]() {  // accumulator fully read: hand it back to the MMA warp
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if (kTwoCta && !leader) ptx::mbar_arrive_remote(acc_empty_bar + acc, 0);
+          else ptx::mbar_arrive(acc_empty_bar + acc);
+        }
       };
 
       if constexpr (kOutF32) {
+        float* dst = static_cast<float*>(p.out) + t.split * p.out_split_stride + out_row * p.n + col0;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = 0; c < kWarpCols / 32; ++c) {
           uint32_t v[32];
           ptx::tmem_ld_32x32b_x32(taddr + c * 32, v);
           ptx::tmem_ld_wait();
-          if (c == BN / 32 - 1) {  // accumulator fully read: hand it back to the MMA warp
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(acc_empty_bar + acc);
-          }
-          uint4* row = reinterpret_cast<uint4*>(my_staging + lane * kStagingRowBytes);
+          if (c == kWarpCols / 32 - 1) release_accumulator();
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             uint4 o;
@@ -374,35 +542,30 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             o.y = empty_split ? 0u : __float_as_uint(__uint_as_float(v[4 * i + 1]) * alpha);
             o.z = empty_split ? 0u : __float_as_uint(__uint_as_float(v[4 * i + 2]) * alpha);
             o.w = empty_split ? 0u : __float_as_uint(__uint_as_float(v[4 * i + 3]) * alpha);
-            row[i] = o;
+            if (row_ok && col0 + c * 32 + 4 * i < p.n) *reinterpret_cast<uint4*>(dst + c * 32 + 4 * i) = o;
           }
-          store_chunk(c);
         }
       } else {
-        uint32_t packed[BN / 2];
+        uint32_t packed[kWarpCols / 2];
 #pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t v[32];
+        for (int c = 0; c < kWarpCols / kLdCols; ++c) {
+          uint32_t v[kLdCols];
           ptx::tmem_ld_32x32b_x32(taddr + c * 32, v);
           ptx::tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            packed[c * 16 + i] = empty_split ? 0u
-                                             : pack_half2(__uint_as_float(v[2 * i]) * alpha,
-                                                          __uint_as_float(v[2 * i + 1]) * alpha);
+          for (int i = 0; i < kLdCols / 2; ++i)
+            packed[c * (kLdCols / 2) + i] =
+                empty_split ? 0u
+                            : pack_half2(__uint_as_float(v[2 * i]) * alpha,
+                                         __uint_as_float(v[2 * i + 1]) * alpha);
         }
-        ptx::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(acc_empty_bar + acc);
+        release_accumulator();
+        __half* dst = static_cast<__half*>(p.out) + t.split * p.out_split_stride + out_row * p.n + col0;
 #pragma unroll
-        for (int chunk = 0; chunk < BN / kChunkCols; ++chunk) {
-          uint4* row = reinterpret_cast<uint4*>(my_staging + lane * kStagingRowBytes);
-#pragma unroll
-          for (int i = 0; i < kChunkBytes / 16; ++i) {
-            const int b = chunk * (kChunkCols / 2) + 4 * i;
-            row[i] = make_uint4(packed[b], packed[b + 1], packed[b + 2], packed[b + 3]);
-          }
-          store_chunk(chunk);
+        for (int i = 0; i < kWarpCols / 8; ++i) {
+          if (row_ok && col0 + 8 * i < p.n)
+            *reinterpret_cast<uint4*>(dst + 8 * i) =
+                make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
         }
       }
       if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
@@ -411,6 +574,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   // ---- teardown
   __syncthreads();
+  // In a pair neither CTA may leave (or free tensor memory) while the other can still
+  // signal its barriers or read its shared memory.
+  if constexpr (kTwoCta) ptx::cluster_sync();
   const int aborted = *abort_flag;
   if (aborted != 0) {
     // give copies that may still be in flight time to land before shared memory goes away
@@ -419,9 +585,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     if (threadIdx.x == 0 && p.error) atomicCAS(p.error, 0, aborted | (static_cast<int>(blockIdx.x) << 8));
   }
-  if (warp == 1) {
+  if (warp == kWarpMma) {
     ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    ptx::tmem_dealloc<kCtas>(tmem_base, Cfg::kTmemCols);
   }
 }
 

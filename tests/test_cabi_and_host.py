@@ -61,7 +61,7 @@ def test_argument_validation_without_gpu():
     assert L.b200_nvfp4_gemm_auto(128, 4096, 8192, 16, 16, 16, 16, 16, None, 0, None) == 3
     assert L.b200_nvfp4_gemm_auto(128, 4096, 8192, 16, 16, 16, 16, 16, 16, 100, None) == 3
     assert L.b200_nvfp4_expert_moe(16, 16, 16, 16, 16, 16, 16, 16, 16, None, 0, 5, 128, 64, 2, 128, None) == 3
-    assert L.b200_nvfp4_set_tile_n(48) == 1 and L.b200_nvfp4_set_tile_n(0) == 0
+    assert L.b200_nvfp4_set_tile_n(48) == 1 and L.b200_nvfp4_set_tile_n(32) == 1 and L.b200_nvfp4_set_tile_n(0) == 0
 
 
 def test_python_surface_mirrors_reference_names():

@@ -45,7 +45,7 @@ def _ones_case(ops, fn, m, n, k):
     assert (got == float(k)).all(), f"{fn.__name__} m={m} n={n} k={k}: {np.unique(got)[:8]}"
 
 
-@pytest.mark.parametrize("tile_n", [0, 32, 64, 128, 256])
+@pytest.mark.parametrize("tile_n", [0, 64, 128, 256, 512])
 def test_all_ones_known_answer(ops, tile_n):
     # tests/python/test_gemm.py:39-68,102-134 (+ K tails and every tile width)
     from sm120_nvfp4_b200 import _lib
@@ -66,7 +66,7 @@ def test_specialized_dispatch_matches_generic(ops):
     _no_device_error()
 
 
-@pytest.mark.parametrize("tile_n", [0, 32, 64, 128, 256])
+@pytest.mark.parametrize("tile_n", [0, 64, 128, 256, 512])
 def test_dyadic_random_payloads_exact(ops, golden_dir, tile_n):
     # tests/python/test_gemm.py:17-37: exact equality with the dequantised matmul
     from sm120_nvfp4_b200 import _lib
@@ -89,7 +89,7 @@ def _random_case(m, n, k, seed):
     return a, sfa, b, sfb
 
 
-@pytest.mark.parametrize("tile_n", [0, 32, 64, 128, 256])
+@pytest.mark.parametrize("tile_n", [0, 64, 128, 256, 512])
 @pytest.mark.parametrize("shape", [(16, 256, 512), (200, 328, 1056), (77, 40, 96), (128, 512, 2048)])
 def test_random_scales_vs_oracle(ops, shape, tile_n):
     # non-uniform per-block scales: exercises the scale layout end to end
@@ -166,7 +166,7 @@ def test_fp32_and_batched_entry_points(ops):
     a, b = _dev(np.stack(As)), _dev(np.stack(Bs))
     sfa, sfb = _dev(np.stack(SAs)), _dev(np.stack(SBs))
     stream = torch.cuda.current_stream().cuda_stream
-    for tile_n in (0, 64, 256):
+    for tile_n in (0, 64, 256, 512):
         L.b200_nvfp4_set_tile_n(tile_n)
         c16 = torch.full((groups, m, n), float("nan"), dtype=torch.float16, device="cuda")
         c32 = torch.full((groups, m, n), float("nan"), dtype=torch.float32, device="cuda")

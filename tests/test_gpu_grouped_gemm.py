@@ -25,7 +25,7 @@ def _dev(x):
     return torch.from_numpy(np.ascontiguousarray(x)).cuda()
 
 
-@pytest.mark.parametrize("tile_n", [0, 32, 64, 128])
+@pytest.mark.parametrize("tile_n", [0, 64, 128, 256, 512])
 def test_empty_experts_tile_tails_and_changed_metadata(ops, golden_dir, tile_n):
     # tests/python/test_grouped_gemm.py:17-52: counts [0,1,127,129] then [129,0,1,127] on the
     # same buffers, NaN-prefilled output, exact equality
