@@ -1,0 +1,377 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 GEMM -> grouped GEMM -> fused-MoE path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload W]
+
+One JSON line on stdout (rank 0). Workloads (synthetic, seeded; no dataset is involved):
+
+  gemm8192      M = N = K = 8192 NVFP4 GEMM, FP16 output (default at N = 1; the shape the
+                headline "% of FP4 peak" target is quoted on)
+  gemm_nshard   M = 16384, N = 28672, K = 8192, B split by columns over the ranks, no
+                collective (default at N > 1; strong scaling)
+  moe           DeepSeek-V3-shaped fused-MoE layer: T = 4096 tokens, hidden 7168,
+                intermediate 2048, 256 experts, top-8; expert-parallel over the ranks with
+                all-to-all dispatch / combine (tokens/s)
+
+A step is one pass of the hot path over one batch. `value` is device-timed with the inputs
+resident in HBM; `e2e` times the same call with host buffers (pinned host -> device copy of
+the step's inputs, the call through the C ABI, device -> host copy of the result). The CPU
+oracle is only ever the thing measured in the `cpu_baseline` / `--impl reference` legs.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+NOMINAL_FP4_TFLOPS = 9000.0      # dense FP4 per B200 (vendor figure without sparsity)
+FALLBACK_BF16_TFLOPS = 1590.0    # earlier pool measurement, used when MEASURED_PEAKS.json is absent
+FALLBACK_HBM_GBS = 6650.0
+
+
+def load_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            d = json.loads(path.read_text())
+            return {"bf16_tflops": float(d["bf16_tflops"]), "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                    "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+        except Exception:
+            pass
+    return {"bf16_tflops": FALLBACK_BF16_TFLOPS, "bf16_tflops_sustained": 1400.0, "hbm_gbs": FALLBACK_HBM_GBS, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._proc = None
+        self._thread = None
+
+    def start(self):
+        query = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+                 "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self._proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={query}",
+                                           "--format=csv,noheader,nounits", "-lms", "20"],
+                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self._proc = None
+            return
+        self._thread = threading.Thread(target=self._read, daemon=True)
+        self._thread.start()
+
+    def _read(self):
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self._proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                self.samples.append((time.time(), float(parts[0])))
+                self.max_mhz = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    self.reasons.add(name)
+
+    def wait_first_sample(self, timeout=5.0):
+        t0 = time.time()
+        while not self.samples and time.time() - t0 < timeout and self._proc is not None:
+            time.sleep(0.02)
+
+    def stop(self, window=None):
+        if self._proc is not None:
+            self._proc.terminate()
+            try:
+                self._proc.wait(timeout=5)
+            except Exception:
+                self._proc.kill()
+        if self._thread is not None:
+            self._thread.join(timeout=5)
+        vals = [v for (t, v) in self.samples if window is None or window[0] <= t <= window[1]]
+        note = "samples inside the timed region"
+        if not vals and self.samples:  # region shorter than the sampling period: nearest sample
+            mid = 0.5 * (window[0] + window[1])
+            vals = [min(self.samples, key=lambda s: abs(s[0] - mid))[1]]
+            note = "timed region shorter than the sampling period: nearest sample"
+        med = float(np.median(vals)) if vals else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(vals), "note": note}
+
+
+# --------------------------------------------------------------------------- data
+
+
+def random_nvfp4(rows: int, k: int, seed: int, device):
+    """Payload / scale bytes with the value statistics of N(0,1) data quantised to NVFP4
+    (codes drawn from the quantiser's output distribution, scale codes around amax/6 of 16
+    normal samples). Generated on the device: the bench times kernels, parity lives in tests/."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    payload = torch.randint(0, 256, (rows, k // 2), dtype=torch.uint8, device=device, generator=g)
+    region = ((rows + 127) // 128 * 128) * (((k + 15) // 16 + 3) // 4 * 4)
+    scales = torch.randint(0x2c, 0x36, (region,), dtype=torch.uint8, device=device, generator=g)
+    return payload, scales
+
+
+def dist_setup(args):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        backend = "nccl" if torch.cuda.is_available() else "gloo"
+        dist.init_process_group(backend, rank=rank, world_size=world)
+    return world, rank, local_rank
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+
+
+def max_over_ranks(value: float, world: int, device) -> float:
+    if world == 1:
+        return value
+    import torch.distributed as dist
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_steps(fn, steps: int, warmup: int, world: int, device, flush: torch.Tensor | None):
+    """W untimed steps, then K steps timed one by one with CUDA events on the current stream
+    (an L2 flush - a write of a buffer larger than L2 - sits between steps, outside the
+    events). Returns mean ms per step as the max over ranks, plus the per-step list."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    barrier(world)
+    torch.cuda.synchronize()
+    per_step = []
+    for _ in range(steps):
+        if flush is not None:
+            flush.zero_()
+        start = torch.cuda.Event(enable_timing=True)
+        end = torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        end.synchronize()
+        per_step.append(start.elapsed_time(end))
+    torch.cuda.synchronize()
+    barrier(world)
+    torch.cuda.synchronize()
+    ms = float(np.mean(per_step))
+    return max_over_ranks(ms, world, device), per_step
+
+
+# ------------------------------------------------------------------------ workloads
+
+
+class GemmWorkload:
+    def __init__(self, m, n_total, k, world, rank, device, name):
+        from sm120_nvfp4_b200 import _lib
+        self.L = _lib.lib()
+        self.m, self.k, self.n_total = m, k, n_total
+        self.n = n_total // world          # this rank's column block of B / C
+        self.name = name
+        self.device = device
+        self.a, self.sfa = random_nvfp4(m, k, 0xB2000500, device)            # A replicated
+        self.b, self.sfb = random_nvfp4(self.n, k, 0xB2000510 + rank, device)  # B shard
+        self.c = torch.empty((m, self.n), dtype=torch.float16, device=device)
+        ws_bytes = self.L.b200_nvfp4_gemm_workspace_bytes(m, self.n, k)
+        self.ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device)
+        self.ws_bytes = ws_bytes
+        self.flops_total = 2.0 * m * n_total * k
+        self.flops_rank = 2.0 * m * self.n * k
+        self.bytes_rank = m * k / 2 + self.n * k / 2 + self.sfa.numel() + self.sfb.numel() + 2 * m * self.n
+        self.host = None
+
+    def step(self):
+        st = torch.cuda.current_stream().cuda_stream
+        status = self.L.b200_nvfp4_gemm_auto(self.m, self.n, self.k, self.a.data_ptr(), self.b.data_ptr(),
+                                             self.sfa.data_ptr(), self.sfb.data_ptr(), self.c.data_ptr(),
+                                             self.ws.data_ptr(), self.ws_bytes, st)
+        if status != 0:
+            raise RuntimeError(f"gemm failed with status {status}")
+
+    def launches_per_step(self):
+        return 2 if self.ws_bytes else 1
+
+    def prepare_e2e(self):
+        self.host = {name: torch.empty(t.shape, dtype=t.dtype).pin_memory().copy_(t.cpu())
+                     for name, t in (("a", self.a), ("b", self.b), ("sfa", self.sfa), ("sfb", self.sfb))}
+        self.host_c = torch.empty(self.c.shape, dtype=self.c.dtype).pin_memory()
+        self.h2d = sum(t.numel() * t.element_size() for t in self.host.values())
+        self.d2h = self.host_c.numel() * self.host_c.element_size()
+
+    def step_e2e(self):
+        self.a.copy_(self.host["a"], non_blocking=True)
+        self.b.copy_(self.host["b"], non_blocking=True)
+        self.sfa.copy_(self.host["sfa"], non_blocking=True)
+        self.sfb.copy_(self.host["sfb"], non_blocking=True)
+        self.step()
+        self.host_c.copy_(self.c, non_blocking=True)
+
+    def metric(self, ms):
+        return self.flops_total / (ms * 1e-3) / 1e12
+
+
+def run_gemm(args, world, rank, device, peaks):
+    if args.workload == "gemm8192":
+        wl = GemmWorkload(8192, 8192 * world, 8192, world, rank, device, "gemm_m8192_n8192_k8192")
+        scaling = "weak"
+    else:
+        wl = GemmWorkload(16384, 28672, 8192, world, rank, device, "gemm_nsharded_m16384_n28672_k8192")
+        scaling = "strong"
+    from sm120_nvfp4_b200 import _lib
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    sampler = ClockSampler(torch.cuda.current_device())
+    launches0 = _lib.launch_count()
+    sampler.start()
+    sampler.wait_first_sample()
+    t_begin = time.time()
+    ms, per_step = time_steps(wl.step, args.steps, args.warmup, world, device, flush)
+    clocks = sampler.stop((t_begin, time.time()))
+    launches = _lib.launch_count() - launches0 - args.warmup * wl.launches_per_step()
+    value = wl.metric(ms)
+
+    wl.prepare_e2e()
+    ms_e2e, _ = time_steps(wl.step_e2e, max(3, min(args.steps, 10)), 3, world, device, None)
+    e2e_value = wl.metric(ms_e2e)
+
+    fp4_peak = 4.0 * peaks["bf16_tflops"]
+    achieved = wl.flops_rank / (float(np.mean(per_step)) * 1e-3) / 1e12
+    line = {
+        "metric": "NVFP4 GEMM TFLOPS (% FP4 peak); fused-MoE tokens/s at 1/2/4/8 B200",
+        "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+        "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate, fp16 out)", "data": "synthetic",
+        "config": {"workload": wl.name, "m": wl.m, "n": wl.n_total, "k": wl.k, "n_per_rank": wl.n,
+                   "l2": "256 MiB flush write between timed steps"},
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
+                "ms_per_step": ms_e2e},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s",
+                     "frac": achieved / fp4_peak, "traffic": None,
+                     "peak_source": f"4 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']:.0f} TF/s): "
+                                    "no FP4 figure is measured on this pool; FP4 : BF16 nominal ratio is 4",
+                     "frac_of_nominal_9pf": achieved / NOMINAL_FP4_TFLOPS,
+                     "kernel": "nvfp4_gemm_kernel"},
+    }
+    return line
+
+
+def cpu_gemm_sample(m, n, k, rows, cols, seed=0xB2000900):
+    """Times the CPU oracle on `rows` x `cols` outputs of an M x N x K problem (all host
+    threads). Returns (tflops, seconds, cores)."""
+    import oracle
+    rng = np.random.default_rng(seed)
+    a = rng.integers(0, 256, (rows, k // 2), dtype=np.uint8)
+    b = rng.integers(0, 256, (cols, k // 2), dtype=np.uint8)
+    sfa = rng.integers(0x2c, 0x36, oracle.scale_region_bytes(rows, k), dtype=np.uint8)
+    sfb = rng.integers(0x2c, 0x36, oracle.scale_region_bytes(cols, k), dtype=np.uint8)
+    oracle.gemm_sampled(a[:8], b[:64], sfa, sfb, np.arange(8, dtype=np.int32), np.arange(64, dtype=np.int32))
+    t0 = time.perf_counter()
+    oracle.gemm_sampled(a, b, sfa, sfb, np.arange(rows, dtype=np.int32), np.arange(cols, dtype=np.int32))
+    dt = time.perf_counter() - t0
+    return 2.0 * rows * cols * k / dt / 1e12, dt, oracle.lib().oracle_num_threads()
+
+
+def run_reference(args, world, rank):
+    """The reference's own CPU implementation of the path = the CPU oracle (the reference's
+    kernels are SM120-only and its CPU reference GEMM lives inside a CUDA test main(), so the
+    restatement in oracle/ is what can run): each step is a bounded sample of the workload."""
+    if rank != 0:
+        return None
+    if args.workload == "gemm8192":
+        name, (m, n, k) = "gemm_m8192_n8192_k8192", (8192, 8192 * world, 8192)
+    else:
+        name, (m, n, k) = "gemm_nsharded_m16384_n28672_k8192", (16384, 28672, 8192)
+    rows, cols = 256, 8192
+    per = []
+    cores = 1
+    for i in range(args.warmup + args.steps):
+        tf, dt, cores = cpu_gemm_sample(m, n, k, rows, cols)
+        if i >= args.warmup:
+            per.append(tf)
+    value = float(np.mean(per))
+    sample = f"{rows} rows x {cols} columns of the {m}x{n}x{k} problem per step"
+    return {
+        "impl": "reference", "metric": "NVFP4 GEMM TFLOPS (% FP4 peak); fused-MoE tokens/s at 1/2/4/8 B200",
+        "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 2.0 * m * n * k / (value * 1e12) * 1e3, "higher_is_better": True,
+        "scaling": "weak" if args.workload == "gemm8192" else "strong", "vs_baseline": None,
+        "dtype": "nvfp4 (e2m1 x ue4m3, exact block sums, fp16 out)", "data": "synthetic",
+        "config": {"workload": name, "m": m, "n": n, "k": k},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=[None, "gemm8192", "gemm_nshard", "moe"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    env_world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.workload is None:
+        args.workload = "gemm8192" if max(args.gpus, env_world) == 1 else "gemm_nshard"
+
+    if args.impl == "reference":
+        rank = int(os.environ.get("RANK", "0"))
+        line = run_reference(args, max(args.gpus, env_world), rank)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    world, rank, local_rank = dist_setup(args)
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    peaks = load_peaks()
+    if args.workload == "moe":
+        from sm120_nvfp4_b200 import bench_moe
+        line = bench_moe.run(args, world, rank, device, peaks, time_steps, ClockSampler)
+    else:
+        line = run_gemm(args, world, rank, device, peaks)
+    if rank == 0 and world == 1:
+        tf, dt, cores = cpu_gemm_sample(line["config"]["m"], line["config"]["n"], line["config"]["k"], 4096, 8192)
+        line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                "sample": f"4096 rows x 8192 columns of the problem, {dt:.1f} s of CPU oracle time"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

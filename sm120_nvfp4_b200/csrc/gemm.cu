@@ -106,7 +106,9 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   p.cu_tiles_out = s.cu_tiles_out;
   p.error = device_error_word();
   p.num_stages = Cfg::stages_for(s.num_groups);
-  { const char* e = std::getenv("B200_NVFP4_DEBUG"); p.debug = e ? std::atoi(e) : 0; }
+  p.num_sf_slots = Cfg::sf_slots_for(s.num_groups);
+  static const int debug_flags = [] { const char* e = std::getenv("B200_NVFP4_DEBUG"); return e ? std::atoi(e) : 0; }();
+  p.debug = debug_flags;
   p.trace = nullptr;
   if (p.debug & 64) { void* tp = nullptr; if (cudaGetSymbolAddress(&tp, g_trace) == cudaSuccess) p.trace = static_cast<unsigned long long*>(tp); }
 
@@ -136,8 +138,7 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
       if (cudaOccupancyMaxActiveClusters(&n, kernel, &probe) != cudaSuccess || n < 1) n = dev.sm_count / 2;
       max_pairs[dev.device] = n;
     });
-    if (p.debug & 16) fprintf(stderr, "max active pairs = %d (sm_count %d)\n", max_pairs[dev.device], dev.sm_count);
-    if (!(p.debug & 32) && workers > max_pairs[dev.device]) workers = max_pairs[dev.device];
+    if (workers > max_pairs[dev.device]) workers = max_pairs[dev.device];
   }
   if (s.exact_m_tiles && tasks < workers) workers = static_cast<int>(tasks);
   if (workers < 1) workers = 1;
@@ -173,7 +174,7 @@ int pick_tile(const LaunchSpec& s, const DeviceInfo& dev) {
   const long long splits = s.num_splits;
   auto tasks = [&](int bn) { return mt * ((s.n + bn - 1) / bn) * splits; };
   if (!s.out_f32 && splits == 1 && ((mt + 1) / 2) * ((s.n + 255) / 256) >= dev.sm_count / 2) return 512;
-  if (tasks(256) >= dev.sm_count) return 256;
+  if (tasks(256) >= dev.sm_count * 2 / 3) return 256;
   if (tasks(128) >= dev.sm_count * 3 / 4) return 128;
   return 64;
 }

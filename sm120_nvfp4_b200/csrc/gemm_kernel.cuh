@@ -61,7 +61,8 @@ constexpr int kFirstSfMoverWarp = 4;    // four warps, one per TMEM lane quarter
 constexpr int kFirstEpilogueWarp = 8;
 constexpr int kGemmThreads = 32 * (kFirstEpilogueWarp + kEpilogueWarps);
 constexpr int kMaxStages = 8;
-constexpr int kBarrierBytes = 384;      // 4 x kMaxStages + 4 mbarriers, TMEM base, abort flag
+constexpr int kMaxSfSlots = 16;
+constexpr int kBarrierBytes = 512;      // 2 x kMaxStages + 2 x kMaxSfSlots + 4 mbarriers, TMEM base, abort flag
 constexpr int kSmemBudget = 232448;     // 227 KB opt-in limit per CTA
 
 struct GemmParams {
@@ -84,8 +85,9 @@ struct GemmParams {
   int* tiles_out;             // optional [G]   ceil(rows/128) per group
   int* cu_tiles_out;          // optional [G+1] exclusive prefix of tiles_out
   int* error;                 // device word that receives a non-zero code on a timed-out wait
-  int num_stages;             // depth of the shared-memory ring (host-computed, <= kMaxStages)
-  int debug;                  // experiment switches (0 in production)
+  int num_stages;             // depth of the operand ring in shared memory (<= kMaxStages)
+  int num_sf_slots;           // depth of the scale-atom ring in shared memory (<= kMaxSfSlots)
+  int debug;                  // bit 64: record time stamps into `trace` (0 in production)
   unsigned long long* trace;  // optional time-stamp buffer (debug bit 64), else nullptr
 };
 
@@ -113,19 +115,29 @@ struct GemmCfg {
   static constexpr int kBBytes = kBRows * kStageKBytes;
   static constexpr int kSfaBytes = 4 * kAtomBytes;
   static constexpr int kSfbBytes = kSfbGroups * 4 * kAtomBytes;
-  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;       // one stage of the operand ring
+  static constexpr int kSfSlotBytes = kSfaBytes + kSfbBytes;  // one slot of the scale-atom ring
 
-  // Shared memory: [stages][barriers][group tables]; +1024 slack to align the base.
+  // Shared memory: [operand stages][scale slots][barriers][group tables]; +1024 slack to align
+  // the base. The scale atoms have a ring of their own: a slot is free again as soon as the
+  // movers have read it into registers, so scale loads (small, long-latency bulk copies) run
+  // well ahead of the operand ring instead of waiting for MMAs to release a stage.
   static constexpr int fixed_bytes(int num_groups) {
     return 1024 + kBarrierBytes + 3 * (num_groups + 1) * 4;
   }
   static constexpr int stages_for(int num_groups) {
-    int s = (kSmemBudget - fixed_bytes(num_groups)) / kStageBytes;
+    // keep room for at least as many scale slots as operand stages
+    int s = (kSmemBudget - fixed_bytes(num_groups)) / (kStageBytes + kSfSlotBytes);
     s = s > kMaxStages ? kMaxStages : s;
     return s > kMaxSfBufs ? kMaxSfBufs : s;
   }
+  static constexpr int sf_slots_for(int num_groups) {
+    int n = (kSmemBudget - fixed_bytes(num_groups) - stages_for(num_groups) * kStageBytes) / kSfSlotBytes;
+    return n > kMaxSfSlots ? kMaxSfSlots : n;
+  }
   static constexpr int smem_bytes(int num_groups) {
-    return fixed_bytes(num_groups) + stages_for(num_groups) * kStageBytes;
+    return fixed_bytes(num_groups) + stages_for(num_groups) * kStageBytes +
+           sf_slots_for(num_groups) * kSfSlotBytes;
   }
   static_assert(stages_for(kMaxGroups) >= 3, "pipeline too shallow");
 };
@@ -168,12 +180,6 @@ __device__ __forceinline__ void trace_stamp(const GemmParams& p, int role, int i
   }
 }
 
-// Fine-grained stamps of the MMA issuer: trace[1024 + iter * 16 + k].
-__device__ __forceinline__ void trace_fine(const GemmParams& p, int iter, int k) {
-  if ((p.debug & 256) && p.trace != nullptr && blockIdx.x == 0 && iter < 60)
-    p.trace[1024 + iter * 16 + k] = static_cast<unsigned long long>(clock64());
-}
-
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -193,15 +199,20 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* stage_base = smem;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
-  // full:      A / B tiles of the stage landed (pair: in both CTAs; lives in the first CTA)
+  const int kSfSlots = p.num_sf_slots;
+  uint8_t* sf_base = smem + kStages * Cfg::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sf_base + kSfSlots * Cfg::kSfSlotBytes);
+  // full:      the stage is ready for the MMAs: its A / B tiles landed in shared memory and
+  //            its scales are in tensor memory (pair: in both CTAs; lives in the first CTA).
+  //            One barrier, because every wait costs the MMA issuer ~150 cycles of a
+  //            ~520-cycle stage.
   // empty:     the MMAs that read the stage are done
-  // sf_landed: the stage's scale atoms landed in this CTA's shared memory
-  // sf_full:   the stage's scales are in tensor memory (pair: of both CTAs; first CTA's)
+  // sf_landed: a slot of the scale ring received its atoms
+  // sf_free:   the four mover warps have read the slot into registers
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* sf_landed_bar = empty_bar + kMaxStages;
-  uint64_t* sf_full_bar = sf_landed_bar + kMaxStages;
-  uint64_t* acc_full_bar = sf_full_bar + kMaxStages;
+  uint64_t* sf_free_bar = sf_landed_bar + kMaxSfSlots;
+  uint64_t* acc_full_bar = sf_free_bar + kMaxSfSlots;
   uint64_t* acc_empty_bar = acc_full_bar + 2;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
   int* abort_flag = reinterpret_cast<int*>(tmem_holder + 1);
@@ -228,10 +239,13 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
-      ptx::mbar_init(full_bar + s, 2);  // the A loader and the B loader of the owning CTA
+      // arrivals: the A and the B loader of the owning CTA + every scale-mover warp
+      ptx::mbar_init(full_bar + s, 2 + 4 * kCtas);
       ptx::mbar_init(empty_bar + s, 1);
+    }
+    for (int s = 0; s < kSfSlots; ++s) {
       ptx::mbar_init(sf_landed_bar + s, 1);
-      ptx::mbar_init(sf_full_bar + s, 4 * kCtas);  // one arrival per mover warp
+      ptx::mbar_init(sf_free_bar + s, 4);
     }
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(acc_full_bar + s, 1);
@@ -297,13 +311,13 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // One thread per operand. Completion bytes are counted on the barrier of the first CTA
     // (in a pair both CTAs' loads report there, and only the first CTA's loader arms it, for
     // both halves), so the MMA issuer waits on one barrier per stage.
-    if (lane == 0) {
+    {
       const bool is_a = warp == kWarpLoadA;
       const CUtensorMap* tmap = is_a ? &tmap_a : &tmap_b;
       const uint32_t bytes = is_a ? Cfg::kABytes : Cfg::kBBytes;
       int stage = 0, iter = 0;
       uint32_t phase = 0;
-      bool ok = true;
+      bool ok = true, peeked = false;
       for (int task = worker; task < total_tasks && ok; task += num_workers) {
         TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
         const int row = is_a ? s_row0[t.g] + t.mt * kTileM + static_cast<int>(cta_rank) * kBlockM
@@ -311,28 +325,33 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int ks_begin = (k_stages * t.split) / p.num_splits;
         const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
         for (int ks = ks_begin; ks < ks_end; ++ks) {
-          if (is_a) trace_stamp(p, 0, iter, 0);
-          if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, 1)) { ok = false; break; }
-          if (is_a) trace_stamp(p, 0, iter++, 1);
+          if (is_a && lane == 0) trace_stamp(p, 0, iter, 0);
+          if (!peeked && !ptx::mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, 1)) { ok = false; break; }
+          if (is_a && lane == 0) trace_stamp(p, 0, iter, 1);
+          ++iter;
           uint8_t* dst = stage_base + stage * Cfg::kStageBytes + (is_a ? 0 : Cfg::kABytes);
-          if constexpr (kTwoCta) {
-            if (leader) ptx::mbar_arrive_expect_tx(full_bar + stage, 2 * bytes);
-            ptx::tma_load_2d_pair(dst, tmap, ptx::map_to_cta(full_bar + stage, 0), ks * kStageKBytes, row);
-          } else {
-            ptx::mbar_arrive_expect_tx(full_bar + stage, bytes);
-            ptx::tma_load_2d(dst, tmap, full_bar + stage, ks * kStageKBytes, row);
+          if (ptx::elect_one()) {
+            if constexpr (kTwoCta) {
+              if (leader) ptx::mbar_arrive_expect_tx(full_bar + stage, 2 * bytes);
+              ptx::tma_load_2d_pair(dst, tmap, ptx::map_to_cta(full_bar + stage, 0), ks * kStageKBytes, row);
+            } else {
+              ptx::mbar_arrive_expect_tx(full_bar + stage, bytes);
+              ptx::tma_load_2d(dst, tmap, full_bar + stage, ks * kStageKBytes, row);
+            }
           }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
+          // probe the next stage now; the answer is used at the top of the next iteration
+          peeked = __all_sync(0xffffffffu, ptx::mbar_test_wait(empty_bar + stage, phase ^ 1));
         }
       }
     }
     __syncwarp();
   } else if (warp == kWarpLoadSf) {
     // ============================== scale loader =============================
-    // The scale atoms are small and sit on a barrier of their own, so their trip into
-    // tensor memory overlaps the (longer) flight of the operand tiles.
-    if (lane == 0) {
-      int stage = 0;
+    // Fills the scale-atom ring: waits for a slot the movers have drained, then bulk-copies
+    // the k-stage's SFA atoms and SFB atoms into it.
+    {
+      int stage = 0, iter = 0;
       uint32_t phase = 0;
       bool ok = true;
       for (int task = worker; task < total_tasks && ok; task += num_workers) {
@@ -348,31 +367,36 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int ks_begin = (k_stages * t.split) / p.num_splits;
         const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
         for (int ks = ks_begin; ks < ks_end; ++ks) {
-          if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, 8)) { ok = false; break; }
-          uint8_t* ssfa = stage_base + stage * Cfg::kStageBytes + Cfg::kABytes + Cfg::kBBytes;
+          if (!ptx::mbar_wait(sf_free_bar + stage, phase ^ 1, abort_flag, 8)) { ok = false; break; }
+          if (lane == 0) trace_stamp(p, 2, iter, 0);
+          uint8_t* ssfa = sf_base + stage * Cfg::kSfSlotBytes;
           uint8_t* ssfb = ssfa + Cfg::kSfaBytes;
           const int atoms = min(4, kt - ks * 4);
           const uint32_t sf_bytes = static_cast<uint32_t>(atoms) * kAtomBytes;
-          ptx::mbar_arrive_expect_tx(sf_landed_bar + stage, sf_bytes * (1 + sfb_groups));
-          ptx::bulk_load(ssfa, sfa_tile + static_cast<long long>(ks) * 4 * kAtomBytes, sf_bytes,
-                         sf_landed_bar + stage);
-          for (int gi = 0; gi < sfb_groups; ++gi)
-            ptx::bulk_load(ssfb + gi * 4 * kAtomBytes,
-                           sfb_tile + (static_cast<long long>(gi) * kt + ks * 4) * kAtomBytes,
-                           sf_bytes, sf_landed_bar + stage);
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          if (ptx::elect_one()) {
+            ptx::mbar_arrive_expect_tx(sf_landed_bar + stage, sf_bytes * (1 + sfb_groups));
+            ptx::bulk_load(ssfa, sfa_tile + static_cast<long long>(ks) * 4 * kAtomBytes, sf_bytes,
+                           sf_landed_bar + stage);
+            for (int gi = 0; gi < sfb_groups; ++gi)
+              ptx::bulk_load(ssfb + gi * 4 * kAtomBytes,
+                             sfb_tile + (static_cast<long long>(gi) * kt + ks * 4) * kAtomBytes,
+                             sf_bytes, sf_landed_bar + stage);
+          }
+          if (lane == 0) trace_stamp(p, 2, iter, 1);
+          ++iter;
+          if (++stage == kSfSlots) { stage = 0; phase ^= 1; }
         }
       }
     }
     __syncwarp();
   } else if (warp == kWarpMma) {
     // =============================== MMA issuer ==============================
-    if (lane == 0 && leader) {
+    if (leader) {
       constexpr uint32_t idesc = ptx::make_idesc_nvfp4(kTileM, BN);
       constexpr uint16_t kAllCtas = kTwoCta ? 3 : 1;
       int stage = 0, acc = 0, iter = 0;
       uint32_t phase = 0, acc_phase = 0;
-      bool ok = true;
+      bool ok = true, peeked = false;
       for (int task = worker; task < total_tasks && ok; task += num_workers) {
         TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
         const int ks_begin = (k_stages * t.split) / p.num_splits;
@@ -384,81 +408,74 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         ptx::tc_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int ks = ks_begin; ks < ks_end; ++ks) {
-          trace_stamp(p, 1, iter, 0);
-          trace_fine(p, iter, 0);
-          if (!ptx::mbar_wait(sf_full_bar + stage, phase, abort_flag, 3)) { ok = false; break; }
-          trace_stamp(p, 3, iter, 0);
-          trace_fine(p, iter, 1);
-          if (!ptx::mbar_wait(full_bar + stage, phase, abort_flag, 7)) { ok = false; break; }
-          trace_stamp(p, 1, iter, 1);
-          trace_fine(p, iter, 2);
+          // The stage was probed while the previous stage's MMAs were being issued; only
+          // fall back to a real wait when that probe came too early.
+          if (lane == 0) trace_stamp(p, 1, iter, 0);
+          if (!peeked && !ptx::mbar_wait(full_bar + stage, phase, abort_flag, 3)) { ok = false; break; }
+          if (lane == 0) trace_stamp(p, 1, iter, 1);
           ptx::tc_fence_after_sync();
-          trace_fine(p, iter, 3);
+          const int next_stage = stage + 1 == kStages ? 0 : stage + 1;
+          peeked = __all_sync(0xffffffffu, ptx::mbar_test_wait(full_bar + next_stage, next_stage == 0 ? phase ^ 1 : phase));
           const uint32_t a_addr = ptx::smem_u32(stage_base + stage * Cfg::kStageBytes);
           const uint32_t b_addr = a_addr + Cfg::kABytes;
           const int atoms = min(4, kt - ks * 4);
           const uint32_t sfa_col = tmem_base + Cfg::kSfBase + stage * Cfg::kSfColsPerBuf;
-          const uint32_t sfb_col = sfa_col + 16;
+          const uint32_t sfb_col = sfa_col + 16 + sfb_sub;
           const uint64_t a_desc = ptx::make_kmajor_sw128_desc(a_addr);
           const uint64_t b_desc = ptx::make_kmajor_sw128_desc(b_addr);
-          if ((p.debug & 128) && iter == 1 && p.trace != nullptr && blockIdx.x == 0) {
-            // micro-benchmark: 64 MMAs back to back on this stage, timed to completion
-            const long long t0 = clock64();
-            for (int rep = 0; rep < 16; ++rep)
-              for (int j = 0; j < 4; ++j)
-                ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_desc + 2 * j, b_desc + 2 * j, idesc,
-                                         sfa_col + 4 * j, sfb_col + j * Cfg::kSfbColsPerMma, 1u);
-            const long long t1 = clock64();
-            ptx::tc_commit<kCtas>(acc_full_bar + 1, 1);   // spare barrier (single accumulator stage)
-            ptx::mbar_wait(acc_full_bar + 1, 0, abort_flag, 9);
-            const long long t2 = clock64();
-            p.trace[2040] = static_cast<unsigned long long>(t1 - t0);
-            p.trace[2041] = static_cast<unsigned long long>(t2 - t0);
-          }
-          if (!(p.debug & 2))
-          for (int j = 0; j < atoms; ++j) {
+          const uint32_t accumulate_first = ks > ks_begin ? 1u : 0u;
+          if (ptx::elect_one()) {
             // 64 E2M1 values = 32 bytes along K: +2 in the descriptor's 16-byte address field
-            ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_desc + 2 * j, b_desc + 2 * j, idesc,
-                                     sfa_col + 4 * j, sfb_col + j * Cfg::kSfbColsPerMma + sfb_sub,
-                                     (ks > ks_begin || j > 0) ? 1u : 0u);
-            trace_fine(p, iter, 4 + j);
+            if (atoms == 4) {
+              ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_desc, b_desc, idesc, sfa_col, sfb_col, accumulate_first);
+              ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_desc + 2, b_desc + 2, idesc, sfa_col + 4,
+                                       sfb_col + Cfg::kSfbColsPerMma, 1u);
+              ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_desc + 4, b_desc + 4, idesc, sfa_col + 8,
+                                       sfb_col + 2 * Cfg::kSfbColsPerMma, 1u);
+              ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_desc + 6, b_desc + 6, idesc, sfa_col + 12,
+                                       sfb_col + 3 * Cfg::kSfbColsPerMma, 1u);
+            } else {
+              for (int j = 0; j < atoms; ++j)
+                ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_desc + 2 * j, b_desc + 2 * j, idesc,
+                                         sfa_col + 4 * j, sfb_col + j * Cfg::kSfbColsPerMma,
+                                         j > 0 ? 1u : accumulate_first);
+            }
+            ptx::tc_commit<kCtas>(empty_bar + stage, kAllCtas);
           }
-          ptx::tc_commit<kCtas>(empty_bar + stage, kAllCtas);
-          trace_fine(p, iter, 8);
-          trace_stamp(p, 3, iter++, 1);
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          ++iter;
+          stage = next_stage;
+          if (stage == 0) phase ^= 1;
         }
         if (!ok) break;
-        ptx::tc_commit<kCtas>(acc_full_bar + acc, kAllCtas);
+        if (ptx::elect_one()) ptx::tc_commit<kCtas>(acc_full_bar + acc, kAllCtas);
         if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
       }
     }
     __syncwarp();
   } else if (warp >= kFirstSfMoverWarp && warp < kFirstSfMoverWarp + 4) {
     // ============================== scale movers =============================
-    // Warp q moves the stage's scale atoms from shared memory into lanes 32q..32q+31 of the
-    // stage's tensor-memory buffer (the MMA wants every 32-lane quarter to hold the same 16
-    // bytes per lane: row r of an atom lives in lane r % 32, column r / 32). Lane t reads
-    // the 16 bytes at offset 16 t of each atom. sf_landed[stage] completing also means the
-    // MMAs that last read this buffer are done (the loader refilled the stage only after).
+    // Warp q moves a k-stage's scale atoms from the scale ring in shared memory into lanes
+    // 32q..32q+31 of the stage's tensor-memory buffer (the MMA wants every 32-lane quarter to
+    // hold the same 16 bytes per lane: row r of an atom lives in lane r % 32, column r / 32).
+    // Lane t reads the 16 bytes at offset 16 t of each atom.
     const int q = warp & 3;
-    int stage = 0;
-    uint32_t phase = 0;
+    int stage = 0, slot = 0, iter = 0;
+    uint32_t phase = 0, slot_phase = 0;
     bool ok = true;
     for (int task = worker; task < total_tasks && ok; task += num_workers) {
       TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
       const int ks_begin = (k_stages * t.split) / p.num_splits;
       const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
       for (int ks = ks_begin; ks < ks_end; ++ks) {
-        int landed = 1;
-        if (lane == 0) landed = ptx::mbar_wait(sf_landed_bar + stage, phase, abort_flag, 5) ? 1 : 0;
-        landed = __shfl_sync(0xffffffffu, landed, 0);
-        if (!landed) { ok = false; break; }
-        const uint8_t* ssfa = stage_base + stage * Cfg::kStageBytes + Cfg::kABytes + Cfg::kBBytes + lane * 16;
+        // 1. atoms of this k-stage: shared memory -> registers
+        int go = 1;
+        if (lane == 0) go = ptx::mbar_wait(sf_landed_bar + slot, slot_phase, abort_flag, 5) ? 1 : 0;
+        go = __shfl_sync(0xffffffffu, go, 0);
+        if (!go) { ok = false; break; }
+        if (q == 0 && lane == 0) trace_stamp(p, 3, iter, 0);
+        const uint8_t* ssfa = sf_base + slot * Cfg::kSfSlotBytes + lane * 16;
         const uint8_t* ssfb = ssfa + Cfg::kSfaBytes;
         const int atoms = min(4, kt - ks * 4);
-        const uint32_t sf_taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                                  static_cast<uint32_t>(Cfg::kSfBase + stage * Cfg::kSfColsPerBuf);
         uint32_t ra[16];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -466,7 +483,6 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (j < atoms) v = *reinterpret_cast<const uint4*>(ssfa + j * kAtomBytes);
           ra[4 * j] = v.x; ra[4 * j + 1] = v.y; ra[4 * j + 2] = v.z; ra[4 * j + 3] = v.w;
         }
-        ptx::tmem_st_32x32b_x16(sf_taddr, ra);
         uint32_t rb[4 * Cfg::kSfbColsPerMma];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -478,15 +494,30 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             rb[c] = v.x; rb[c + 1] = v.y; rb[c + 2] = v.z; rb[c + 3] = v.w;
           }
         }
+        // 2. registers -> the stage's tensor-memory buffer, once the MMAs that last read that
+        //    buffer are done (same condition that lets the operand loaders refill the stage)
+        if (lane == 0) go = ptx::mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, 6) ? 1 : 0;
+        go = __shfl_sync(0xffffffffu, go, 0);
+        if (!go) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        const uint32_t sf_taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                  static_cast<uint32_t>(Cfg::kSfBase + stage * Cfg::kSfColsPerBuf);
+        ptx::tmem_st_32x32b_x16(sf_taddr, ra);
         if constexpr (Cfg::kSfbGroups == 2) ptx::tmem_st_32x32b_x32(sf_taddr + 16, rb);
         else ptx::tmem_st_32x32b_x16(sf_taddr + 16, rb);
         ptx::tmem_st_wait();
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
-          if (kTwoCta && !leader) ptx::mbar_arrive_remote(sf_full_bar + stage, 0);
-          else ptx::mbar_arrive(sf_full_bar + stage);
+          if (kTwoCta && !leader) ptx::mbar_arrive_remote(full_bar + stage, 0);
+          else ptx::mbar_arrive(full_bar + stage);
+          // the stores above consumed every lane's registers, so the slot's bytes have
+          // certainly been read: hand it back to the scale loader
+          ptx::mbar_arrive(sf_free_bar + slot);
+          if (q == 0) trace_stamp(p, 3, iter, 1);
         }
+        if (++slot == kSfSlots) { slot = 0; slot_phase ^= 1; }
+        ++iter;
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }

@@ -14,6 +14,21 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// True in exactly one (always the same) lane of a fully active warp. Code that issues
+// single-thread instructions (TMA, tcgen05.mma, tcgen05.commit) keeps the whole warp in
+// uniform control flow and wraps only the instruction in `if (elect_one())`, so the compiler
+// can hold addresses and descriptors in uniform registers instead of moving them there from
+// one lane's registers before every instruction.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---------------------------------------------------------------- mbarrier
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -39,12 +54,24 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                : "memory");
 }
 
-// Acquire at cluster scope: in a CTA pair some arrivals come from the other CTA.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Non-blocking probe of the same condition (never suspends the thread).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)
@@ -251,19 +278,21 @@ __device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t cta_rank)
 // arrive (count 1) + expect `bytes` more transaction bytes on a barrier given by its
 // shared::cluster address (possibly in the other CTA of the cluster).
 __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t bar_cluster_addr, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(
                    bar_cluster_addr),
                "r"(bytes)
                : "memory");
 }
 
 // Arrives (count 1) on the mbarrier at the same shared-memory offset as `bar` in the CTA
-// with rank `cta_rank` of this cluster.
+// with rank `cta_rank` of this cluster. Default (CTA-scope release) semantics: a cluster-scope
+// release costs the arriving thread more than a microsecond, and what these arrivals order -
+// tensor-memory traffic - is ordered by the tcgen05 fences on both sides.
 __device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t cta_rank) {
   asm volatile(
       "{\n\t.reg .b32 raddr;\n\t"
       "mapa.shared::cluster.u32 raddr, %0, %1;\n\t"
-      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [raddr];\n\t}" ::"r"(smem_u32(bar)),
+      "mbarrier.arrive.shared::cluster.b64 _, [raddr];\n\t}" ::"r"(smem_u32(bar)),
       "r"(cta_rank)
       : "memory");
 }
