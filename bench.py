@@ -284,6 +284,119 @@ def run_gemm(args, world, rank, device, peaks):
     return line
 
 
+class MoeWorkload:
+    """DeepSeek-V3-shaped routed MoE layer: T tokens per rank, hidden 7168, intermediate 2048,
+    256 experts, top-8 (sigmoid scores, renormalised weights), NVFP4 weights ~ N(0, 0.02^2)."""
+
+    def __init__(self, tokens, world, rank, device, experts=256, hidden=7168, inter=2048, topk=8):
+        import sm120_nvfp4_b200 as ops
+        from sm120_nvfp4_b200.ep import ExpertParallelMoE
+        self.ops = ops
+        self.t, self.h, self.i, self.e, self.k = tokens, hidden, inter, experts, topk
+        self.world, self.rank, self.device = world, rank, device
+        e_local = experts // world
+        self.e_local = e_local
+        g = torch.Generator(device=device).manual_seed(0xB2000400 + rank)
+
+        def weights(rows, k):
+            payload = torch.randint(0, 256, (e_local, rows, k // 2), dtype=torch.uint8, device=device, generator=g)
+            region = ((rows + 127) // 128 * 128) * (((k + 15) // 16 + 3) // 4 * 4)
+            scale = torch.randint(0x04, 0x0c, (e_local, region), dtype=torch.uint8, device=device, generator=g)
+            return payload, scale
+
+        self.gw, self.gws = weights(2 * inter, hidden)
+        self.dw, self.dws = weights(hidden, inter)
+        self.x = torch.randn((tokens, hidden), device=device, generator=g).to(torch.bfloat16)
+        logits = torch.randn((tokens, experts), device=device, generator=g)
+        scores = torch.sigmoid(logits)
+        top = torch.topk(scores, topk, dim=1)
+        self.ids = top.indices.to(torch.int32).contiguous()
+        self.w = (top.values / top.values.sum(1, keepdim=True)).float().contiguous()
+        self.seq1 = torch.tensor([tokens], dtype=torch.int32, device=device)
+        self.cu1 = torch.tensor([0, tokens], dtype=torch.int32, device=device)
+        self.in_pad = (tokens + 127) // 128 * 128
+        self.layer = ExpertParallelMoE(self.gw, self.gws, self.dw, self.dws, experts) if world > 1 else None
+        self.out = None
+        a = tokens * topk
+        self.flops_rank = 6.0 * a * hidden * inter      # expected share when routing is balanced
+        w_bytes = e_local * (2 * inter * hidden // 2 + hidden * inter // 2)
+        sf_bytes = e_local * (2 * inter * hidden // 16 + hidden * inter // 16)
+        act = (tokens * hidden * 2 + a * (hidden // 2 + hidden // 16) * 2        # quantise + gather
+               + a * (hidden // 2 + hidden // 16) + a * 2 * inter * 2            # gate/up GEMM in/out
+               + a * (4 * inter + inter // 2 + inter // 16)                      # SiLU*up + quant
+               + a * (inter // 2 + inter // 16) + a * hidden * 2                 # down GEMM in/out
+               + tokens * (topk * 2 * hidden + 2 * hidden))                      # combine
+        self.bytes_rank = w_bytes + sf_bytes + act
+
+    def step(self):
+        if self.world == 1:
+            packed, scales = self.ops.quantize_expert(self.x, self.seq1, self.cu1, scale_m_pad=self.in_pad)
+            self.out = self.ops.fused_moe(packed, scales.flatten(), self.gw, self.gws, self.dw, self.dws, self.ids, self.w)
+        else:
+            self.out = self.layer.forward(self.x, self.ids, self.w, out_bf16=True)
+
+    def prepare_e2e(self):
+        self.hx = torch.empty(self.x.shape, dtype=self.x.dtype).pin_memory().copy_(self.x.cpu())
+        self.hids = torch.empty(self.ids.shape, dtype=self.ids.dtype).pin_memory().copy_(self.ids.cpu())
+        self.hw = torch.empty(self.w.shape, dtype=self.w.dtype).pin_memory().copy_(self.w.cpu())
+        self.step()
+        self.hout = torch.empty(self.out.shape, dtype=self.out.dtype).pin_memory()
+        self.h2d = sum(t.numel() * t.element_size() for t in (self.hx, self.hids, self.hw))
+        self.d2h = self.hout.numel() * self.hout.element_size()
+
+    def step_e2e(self):
+        self.x.copy_(self.hx, non_blocking=True)
+        self.ids.copy_(self.hids, non_blocking=True)
+        self.w.copy_(self.hw, non_blocking=True)
+        self.step()
+        self.hout.copy_(self.out, non_blocking=True)
+
+
+def run_moe(args, world, rank, device, peaks):
+    from sm120_nvfp4_b200 import _lib
+    wl = MoeWorkload(4096, world, rank, device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    sampler = ClockSampler(torch.cuda.current_device())
+    steps = min(args.steps, 50)
+    wl.step()
+    torch.cuda.synchronize()
+    launches0 = _lib.launch_count()
+    wl.step()
+    launches_per_step = _lib.launch_count() - launches0
+    sampler.start()
+    sampler.wait_first_sample()
+    t_begin = time.time()
+    ms, per_step = time_steps(wl.step, steps, max(3, min(args.warmup, 5)), world, device, flush)
+    clocks = sampler.stop((t_begin, time.time()))
+    tokens_total = wl.t * world
+    value = tokens_total / (ms * 1e-3)
+    wl.prepare_e2e()
+    ms_e2e, _ = time_steps(wl.step_e2e, 10, 3, world, device, None)
+    achieved_gbs = wl.bytes_rank / (float(np.mean(per_step)) * 1e-3) / 1e9
+    line = {
+        "metric": "NVFP4 GEMM TFLOPS (% FP4 peak); fused-MoE tokens/s at 1/2/4/8 B200",
+        "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": max(3, min(args.warmup, 5)),
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate), bf16 activations", "data": "synthetic",
+        "config": {"workload": "fused_moe_deepseek_v3_shape", "tokens_per_rank": wl.t, "hidden": wl.h,
+                   "intermediate": wl.i, "experts": wl.e, "topk": wl.k, "experts_per_rank": wl.e_local,
+                   "parallelism": f"ep{world}" if world > 1 else "single", "l2": "256 MiB flush write between timed steps"},
+        "e2e": {"value": tokens_total / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": wl.h2d,
+                "d2h_bytes_per_step": wl.d2h, "ms_per_step": ms_e2e},
+        "gpu_launches": int(launches_per_step * steps),
+        "clocks": clocks,
+        "roofline": {"bound": "hbm" if world == 1 else "tensor",
+                     "achieved": achieved_gbs if world == 1 else wl.flops_rank / (float(np.mean(per_step)) * 1e-3) / 1e12,
+                     "peak": peaks["hbm_gbs"] if world == 1 else 4.0 * peaks["bf16_tflops_sustained"],
+                     "unit": "GB/s" if world == 1 else "TFLOP/s", "traffic": None,
+                     "kernel": "whole layer (two grouped nvfp4_gemm_kernel launches dominate)",
+                     "peak_source": peaks["source"]},
+        "tflops_per_rank": wl.flops_rank / (float(np.mean(per_step)) * 1e-3) / 1e12,
+    }
+    line["roofline"]["frac"] = line["roofline"]["achieved"] / line["roofline"]["peak"]
+    return line
+
+
 def cpu_gemm_sample(m, n, k, rows, cols, seed=0xB2000900):
     """Times the CPU oracle on `rows` x `cols` outputs of an M x N x K problem (all host
     threads). Returns (tflops, seconds, cores)."""
@@ -310,7 +423,7 @@ def run_reference(args, world, rank):
         name, (m, n, k) = "gemm_m8192_n8192_k8192", (8192, 8192 * world, 8192)
     else:
         name, (m, n, k) = "gemm_nsharded_m16384_n28672_k8192", (16384, 28672, 8192)
-    rows, cols = 256, 8192
+    rows, cols = 64, 8192
     per = []
     cores = 1
     for i in range(args.warmup + args.steps):
@@ -358,11 +471,10 @@ def main():
     device = torch.device("cuda", local_rank)
     peaks = load_peaks()
     if args.workload == "moe":
-        from sm120_nvfp4_b200 import bench_moe
-        line = bench_moe.run(args, world, rank, device, peaks, time_steps, ClockSampler)
+        line = run_moe(args, world, rank, device, peaks)
     else:
         line = run_gemm(args, world, rank, device, peaks)
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and args.workload != "moe":
         tf, dt, cores = cpu_gemm_sample(line["config"]["m"], line["config"]["n"], line["config"]["k"], 4096, 8192)
         line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                                 "sample": f"4096 rows x 8192 columns of the problem, {dt:.1f} s of CPU oracle time"}

@@ -138,6 +138,34 @@ B200_NVFP4_API int b200_nvfp4_moe_quantize_expert(void* output, void* output_sca
                                                   int grouped_scale_m_pad, int input_is_bf16,
                                                   int zero_scales, b200_stream_t stream);
 
+/* Extension (no counterpart in the reference): quantize_expert that also permutes - grouped
+ * row r is read from input row row_map[r] (int32, may be NULL = identity). Used by the
+ * expert-parallel driver to turn rows received source-major into expert-major NVFP4 in one
+ * pass. */
+B200_NVFP4_API int b200_nvfp4_moe_quantize_expert_gather(void* output, void* output_scale,
+                                                         const void* input, const void* row_map,
+                                                         const void* seqlens, const void* cu_seqlens,
+                                                         int num_expert_local, int total_rows,
+                                                         int hidden_size, int grouped_scale_m_pad,
+                                                         int input_is_bf16, int zero_scales,
+                                                         b200_stream_t stream);
+
+/* Extension: the routing half of count_and_gather alone (src/fused_moe/count_and_gather.cu:
+ * 12-38 plus the slot assignment of :59-64, made deterministic): seqlens[E], cu_seqlens[E+1]
+ * and topk_pos (grouped row of every assignment, -1 for experts outside
+ * [rank_ep*E, rank_ep*E+E)). */
+B200_NVFP4_API int b200_nvfp4_moe_route(const void* topk_ids, void* topk_pos, void* seqlens,
+                                        void* cu_seqlens, int num_tokens, int num_topk,
+                                        int num_expert_local, int rank_ep, b200_stream_t stream);
+
+/* Extension: row movers of the expert-parallel dispatch / combine (rows of row_bytes bytes,
+ * row_bytes % 16 == 0). scatter: dst[pos[a]] = src[a / fanout] for a < count, pos[a] >= 0.
+ * gather: dst[i] = src[map[i]] for i < count, map[i] >= 0. */
+B200_NVFP4_API int b200_nvfp4_moe_scatter_rows(void* dst, const void* src, const void* pos, int count,
+                                               int fanout, int row_bytes, b200_stream_t stream);
+B200_NVFP4_API int b200_nvfp4_moe_gather_rows(void* dst, const void* src, const void* map, int count,
+                                              int row_bytes, b200_stream_t stream);
+
 /* fused_moe::reduce_nvfp4_async (fused_moe.hpp:41-45, src/fused_moe/reduce.cu:39-55):
  * out[t] = half(shared[t] + sum_r w[t,r] * down[pos[t,r]]) in FP32, route order, skipping
  * pos < 0. out_is_bf16 != 0 (extension) rounds the same FP32 sum to BF16 instead. */

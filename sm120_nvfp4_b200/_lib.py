@@ -33,6 +33,10 @@ _SIGNATURES = {
     "b200_nvfp4_moe_count_and_gather": (ci, [vp] * 8 + [ci] * 8 + [vp]),
     "b200_nvfp4_moe_act_mul_and_quant": (ci, [vp] * 5 + [ci] * 5 + [vp]),
     "b200_nvfp4_moe_quantize_expert": (ci, [vp] * 5 + [ci] * 6 + [vp]),
+    "b200_nvfp4_moe_quantize_expert_gather": (ci, [vp] * 6 + [ci] * 6 + [vp]),
+    "b200_nvfp4_moe_route": (ci, [vp] * 4 + [ci] * 4 + [vp]),
+    "b200_nvfp4_moe_scatter_rows": (ci, [vp] * 3 + [ci] * 3 + [vp]),
+    "b200_nvfp4_moe_gather_rows": (ci, [vp] * 3 + [ci] * 2 + [vp]),
     "b200_nvfp4_moe_reduce": (ci, [vp] * 5 + [ci] * 4 + [vp]),
     "b200_nvfp4_fused_moe": (ci, [vp] * 23 + [ci] * 9 + [vp]),
     "b200_nvfp4_expert_moe_workspace_bytes": (C.c_size_t, [ci] * 5),

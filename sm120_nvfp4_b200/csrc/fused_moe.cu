@@ -151,9 +151,40 @@ int b200_nvfp4_moe_quantize_expert(void* output, void* output_scale, const void*
                                    const void* seqlens, const void* cu_seqlens, int num_expert_local,
                                    int total_rows, int hidden_size, int grouped_scale_m_pad,
                                    int input_is_bf16, int zero_scales, b200_stream_t stream) {
-  return b200::moe_quantize_expert(output, output_scale, input, seqlens, cu_seqlens, num_expert_local,
-                                   total_rows, hidden_size, grouped_scale_m_pad, input_is_bf16 != 0,
-                                   zero_scales != 0, static_cast<cudaStream_t>(stream));
+  return b200::moe_quantize_expert(output, output_scale, input, seqlens, cu_seqlens, nullptr,
+                                   num_expert_local, total_rows, hidden_size, grouped_scale_m_pad,
+                                   input_is_bf16 != 0, zero_scales != 0,
+                                   static_cast<cudaStream_t>(stream));
+}
+
+int b200_nvfp4_moe_quantize_expert_gather(void* output, void* output_scale, const void* input,
+                                          const void* row_map, const void* seqlens,
+                                          const void* cu_seqlens, int num_expert_local, int total_rows,
+                                          int hidden_size, int grouped_scale_m_pad, int input_is_bf16,
+                                          int zero_scales, b200_stream_t stream) {
+  return b200::moe_quantize_expert(output, output_scale, input, seqlens, cu_seqlens, row_map,
+                                   num_expert_local, total_rows, hidden_size, grouped_scale_m_pad,
+                                   input_is_bf16 != 0, zero_scales != 0,
+                                   static_cast<cudaStream_t>(stream));
+}
+
+int b200_nvfp4_moe_route(const void* topk_ids, void* topk_pos, void* seqlens, void* cu_seqlens,
+                         int num_tokens, int num_topk, int num_expert_local, int rank_ep,
+                         b200_stream_t stream) {
+  return b200::moe_route(topk_ids, topk_pos, seqlens, cu_seqlens, num_tokens, num_topk,
+                         num_expert_local, rank_ep, static_cast<cudaStream_t>(stream));
+}
+
+int b200_nvfp4_moe_scatter_rows(void* dst, const void* src, const void* pos, int count, int fanout,
+                                int row_bytes, b200_stream_t stream) {
+  return b200::moe_move_rows(dst, src, pos, count, fanout, row_bytes, true,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int b200_nvfp4_moe_gather_rows(void* dst, const void* src, const void* map, int count, int row_bytes,
+                               b200_stream_t stream) {
+  return b200::moe_move_rows(dst, src, map, count, 1, row_bytes, false,
+                             static_cast<cudaStream_t>(stream));
 }
 
 int b200_nvfp4_moe_reduce(void* output, const void* down_output, const void* topk_pos,

@@ -36,9 +36,15 @@ int moe_act_mul_and_quant(void* output, void* output_scale, const void* gate_up,
                           cudaStream_t stream);
 
 int moe_quantize_expert(void* output, void* output_scale, const void* input, const void* seqlens,
-                        const void* cu_seqlens, int num_expert_local, int total_rows, int hidden_size,
-                        int grouped_scale_m_pad, bool input_is_bf16, bool zero_scales,
-                        cudaStream_t stream);
+                        const void* cu_seqlens, const void* row_map, int num_expert_local,
+                        int total_rows, int hidden_size, int grouped_scale_m_pad, bool input_is_bf16,
+                        bool zero_scales, cudaStream_t stream);
+
+int moe_route(const void* topk_ids, void* topk_pos, void* seqlens, void* cu_seqlens, int num_tokens,
+              int num_topk, int num_expert_local, int rank_ep, cudaStream_t stream);
+
+int moe_move_rows(void* dst, const void* src, const void* index, int count, int fanout, int row_bytes,
+                  bool scatter, cudaStream_t stream);
 
 int moe_reduce(void* output, const void* down_output, const void* topk_pos, const void* topk_scale,
                const void* shared_output, int num_tokens, int hidden_size, int num_topk,

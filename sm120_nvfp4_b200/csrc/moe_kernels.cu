@@ -262,8 +262,8 @@ template <int kMode>
 __global__ void __launch_bounds__(256)
 quant_rows_kernel(uint8_t* __restrict__ output, uint8_t* __restrict__ output_scale,
                   const void* __restrict__ input, const int* __restrict__ seqlens,
-                  const int* __restrict__ cu_seqlens, int num_expert, int width,
-                  long long group_scale_stride) {
+                  const int* __restrict__ cu_seqlens, const int* __restrict__ row_map, int num_expert,
+                  int width, long long group_scale_stride) {
   extern __shared__ int s_cu[];
   for (int e = threadIdx.x; e <= num_expert; e += blockDim.x) s_cu[e] = cu_seqlens[e];
   __syncthreads();
@@ -283,18 +283,19 @@ quant_rows_kernel(uint8_t* __restrict__ output, uint8_t* __restrict__ output_sca
     uint8_t code = 0;
     if (live) {
       float v[16];
+      // optional gather: grouped row r is read from input row row_map[r]
+      const long long in_row = row_map ? static_cast<long long>(row_map[grouped_row]) : grouped_row;
       if constexpr (kMode == 0) {
-        const __half* gate = static_cast<const __half*>(input) +
-                             static_cast<long long>(grouped_row) * width * 2 + kb * 16;
+        const __half* gate = static_cast<const __half*>(input) + in_row * width * 2 + kb * 16;
         float g[16], u[16];
         load16(gate, g);
         load16(gate + width, u);
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = __fmul_rn(nvfp4_silu(g[i]), u[i]);
       } else if constexpr (kMode == 1) {
-        load16(static_cast<const __half*>(input) + static_cast<long long>(grouped_row) * width + kb * 16, v);
+        load16(static_cast<const __half*>(input) + in_row * width + kb * 16, v);
       } else {
-        load16(static_cast<const __nv_bfloat16*>(input) + static_cast<long long>(grouped_row) * width + kb * 16, v);
+        load16(static_cast<const __nv_bfloat16*>(input) + in_row * width + kb * 16, v);
       }
       uint32_t lo, hi;
       code = quantize_block16(v, lo, hi);
@@ -377,6 +378,23 @@ reduce_kernel(void* __restrict__ output, const __half* __restrict__ down_output,
   }
 }
 
+__global__ void __launch_bounds__(256)
+move_rows_kernel(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src,
+                 const int* __restrict__ index, int count, int fanout, int row_bytes, bool scatter) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int vecs = row_bytes >> 4;
+  for (int i = blockIdx.x * warps_per_block + (threadIdx.x >> 5); i < count; i += gridDim.x * warps_per_block) {
+    const int idx = index[i];
+    if (idx < 0) continue;
+    const long long src_row = scatter ? i / fanout : idx;
+    const long long dst_row = scatter ? idx : i;
+    const uint4* s4 = reinterpret_cast<const uint4*>(src + src_row * row_bytes);
+    uint4* d4 = reinterpret_cast<uint4*>(dst + dst_row * row_bytes);
+    for (int v = lane; v < vecs; v += 32) d4[v] = s4[v];
+  }
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int check_launch() {
@@ -441,8 +459,8 @@ int moe_count_and_gather(void* gate_up_input, void* gate_up_input_scale, const v
 
 template <int kMode>
 int launch_quant(void* output, void* output_scale, const void* input, const void* seqlens,
-                 const void* cu_seqlens, int num_expert_local, int total_rows, int width,
-                 int grouped_scale_m_pad, bool zero_scales, cudaStream_t stream) {
+                 const void* cu_seqlens, const void* row_map, int num_expert_local, int total_rows,
+                 int width, int grouped_scale_m_pad, bool zero_scales, cudaStream_t stream) {
   if (output == nullptr || output_scale == nullptr || input == nullptr || seqlens == nullptr ||
       cu_seqlens == nullptr || num_expert_local <= 0 || num_expert_local > kMaxExperts ||
       width <= 0 || (width % 32) != 0 || grouped_scale_m_pad < 128 ||
@@ -468,8 +486,8 @@ int launch_quant(void* output, void* output_scale, const void* input, const void
   if (blocks < 1) blocks = 1;
   quant_rows_kernel<kMode><<<static_cast<int>(blocks), 256, (num_expert_local + 1) * sizeof(int), stream>>>(
       static_cast<uint8_t*>(output), static_cast<uint8_t*>(output_scale), input,
-      static_cast<const int*>(seqlens), static_cast<const int*>(cu_seqlens), num_expert_local, width,
-      group_stride);
+      static_cast<const int*>(seqlens), static_cast<const int*>(cu_seqlens),
+      static_cast<const int*>(row_map), num_expert_local, width, group_stride);
   count_launch();
   return check_launch();
 }
@@ -478,19 +496,74 @@ int moe_act_mul_and_quant(void* output, void* output_scale, const void* gate_up,
                           const void* cu_seqlens, int num_expert_local, int total_rows,
                           int grouped_scale_m_pad, int intermediate_size, bool zero_scales,
                           cudaStream_t stream) {
-  return launch_quant<0>(output, output_scale, gate_up, seqlens, cu_seqlens, num_expert_local,
+  return launch_quant<0>(output, output_scale, gate_up, seqlens, cu_seqlens, nullptr, num_expert_local,
                          total_rows, intermediate_size, grouped_scale_m_pad, zero_scales, stream);
 }
 
 int moe_quantize_expert(void* output, void* output_scale, const void* input, const void* seqlens,
-                        const void* cu_seqlens, int num_expert_local, int total_rows, int hidden_size,
-                        int grouped_scale_m_pad, bool input_is_bf16, bool zero_scales,
-                        cudaStream_t stream) {
+                        const void* cu_seqlens, const void* row_map, int num_expert_local,
+                        int total_rows, int hidden_size, int grouped_scale_m_pad, bool input_is_bf16,
+                        bool zero_scales, cudaStream_t stream) {
   return input_is_bf16
-             ? launch_quant<2>(output, output_scale, input, seqlens, cu_seqlens, num_expert_local,
-                               total_rows, hidden_size, grouped_scale_m_pad, zero_scales, stream)
-             : launch_quant<1>(output, output_scale, input, seqlens, cu_seqlens, num_expert_local,
-                               total_rows, hidden_size, grouped_scale_m_pad, zero_scales, stream);
+             ? launch_quant<2>(output, output_scale, input, seqlens, cu_seqlens, row_map,
+                               num_expert_local, total_rows, hidden_size, grouped_scale_m_pad,
+                               zero_scales, stream)
+             : launch_quant<1>(output, output_scale, input, seqlens, cu_seqlens, row_map,
+                               num_expert_local, total_rows, hidden_size, grouped_scale_m_pad,
+                               zero_scales, stream);
+}
+
+// Routing only (no payload movement): seqlens / cu_seqlens / topk_pos as in
+// moe_count_and_gather.
+int moe_route(const void* topk_ids, void* topk_pos, void* seqlens, void* cu_seqlens, int num_tokens,
+              int num_topk, int num_expert_local, int rank_ep, cudaStream_t stream) {
+  const long long total64 = static_cast<long long>(num_tokens) * num_topk;
+  if (topk_ids == nullptr || topk_pos == nullptr || seqlens == nullptr || cu_seqlens == nullptr ||
+      num_tokens <= 0 || num_topk <= 0 || num_expert_local <= 0 || num_expert_local > kMaxExperts ||
+      rank_ep < 0 || total64 > 0x7fffffffLL) {
+    return B200_NVFP4_INVALID_ARGUMENT;
+  }
+  const int total = static_cast<int>(total64);
+  const int start_expert = rank_ep * num_expert_local;
+  const int* ids = static_cast<const int*>(topk_ids);
+  int* pos = static_cast<int*>(topk_pos);
+  int* sl = static_cast<int*>(seqlens);
+  int* cu = static_cast<int*>(cu_seqlens);
+  const int num_chunks = total / kRouteChunk;
+  if (num_chunks <= 1) {
+    route_small_kernel<<<1, kRouteThreads, 0, stream>>>(ids, pos, sl, cu, total, start_expert,
+                                                        num_expert_local);
+    count_launch();
+  } else {
+    route_count_kernel<<<num_chunks, kRouteThreads, 0, stream>>>(ids, pos, total, num_chunks,
+                                                                 start_expert, num_expert_local);
+    route_scan_kernel<<<1, kRouteThreads, 0, stream>>>(pos, sl, cu, num_chunks, num_expert_local);
+    route_rank_kernel<<<num_chunks, kRouteThreads, 0, stream>>>(ids, pos, cu, total, num_chunks,
+                                                                start_expert, num_expert_local);
+    count_launch(3);
+  }
+  return check_launch();
+}
+
+// Row movers of the expert-parallel driver (16-byte vectors, one warp per row).
+//   scatter: dst[pos[a]] = src[a / fanout]   for every a < count with pos[a] >= 0
+//   gather:  dst[i]      = src[map[i]]       for every i < count with map[i] >= 0
+int moe_move_rows(void* dst, const void* src, const void* index, int count, int fanout, int row_bytes,
+                  bool scatter, cudaStream_t stream) {
+  if (dst == nullptr || src == nullptr || index == nullptr || count <= 0 || fanout <= 0 ||
+      row_bytes <= 0 || (row_bytes % 16) != 0 || !aligned16(dst) || !aligned16(src)) {
+    return B200_NVFP4_INVALID_ARGUMENT;
+  }
+  const DeviceInfo& dev = current_device_info();
+  if (!dev.ok) return B200_NVFP4_CUDA_ERROR;
+  int blocks = (count + 7) / 8;
+  const int max_blocks = dev.sm_count * 8;
+  if (blocks > max_blocks) blocks = max_blocks;
+  move_rows_kernel<<<blocks, 256, 0, stream>>>(static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src),
+                                               static_cast<const int*>(index), count, fanout, row_bytes,
+                                               scatter);
+  count_launch();
+  return check_launch();
 }
 
 int moe_reduce(void* output, const void* down_output, const void* topk_pos, const void* topk_scale,
