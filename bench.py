@@ -9,6 +9,7 @@ One JSON line on stdout (rank 0). Workloads (synthetic, seeded; no dataset is in
                 headline "% of FP4 peak" target is quoted on)
   gemm_nshard   M = 16384, N = 28672, K = 8192, B split by columns over the ranks, no
                 collective (default at N > 1; strong scaling)
+  gemm4096      M = N = 4096, K = 8192: a small case of the same kernel for profiler captures
   moe           DeepSeek-V3-shaped fused-MoE layer: T = 4096 tokens, hidden 7168,
                 intermediate 2048, 256 experts, top-8; expert-parallel over the ranks with
                 all-to-all dispatch / combine (tokens/s)
@@ -242,6 +243,9 @@ def run_gemm(args, world, rank, device, peaks):
     if args.workload == "gemm8192":
         wl = GemmWorkload(8192, 8192 * world, 8192, world, rank, device, "gemm_m8192_n8192_k8192")
         scaling = "weak"
+    elif args.workload == "gemm4096":   # small case of the same kernel, for profiler captures
+        wl = GemmWorkload(4096, 4096 * world, 8192, world, rank, device, "gemm_m4096_n4096_k8192")
+        scaling = "weak"
     else:
         wl = GemmWorkload(16384, 28672, 8192, world, rank, device, "gemm_nsharded_m16384_n28672_k8192")
         scaling = "strong"
@@ -450,7 +454,7 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=[None, "gemm8192", "gemm_nshard", "moe"])
+    ap.add_argument("--workload", default=None, choices=[None, "gemm8192", "gemm4096", "gemm_nshard", "moe"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     env_world = int(os.environ.get("WORLD_SIZE", "1"))

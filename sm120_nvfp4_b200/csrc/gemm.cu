@@ -62,6 +62,7 @@ struct LaunchSpec {
   int* cu_tiles_out;
   int expected_m_tiles;    // estimate used to pick the tile width and the grid
   bool exact_m_tiles;      // expected_m_tiles is exact (dense) rather than a hint (grouped)
+  int avg_group_rows;      // rows per group (exact for dense, a hint for grouped)
 };
 
 template <int BN, bool F32, bool kTwoCta>
@@ -173,7 +174,12 @@ int pick_tile(const LaunchSpec& s, const DeviceInfo& dev) {
   const long long mt = s.expected_m_tiles > 0 ? s.expected_m_tiles : 1;
   const long long splits = s.num_splits;
   auto tasks = [&](int bn) { return mt * ((s.n + bn - 1) / bn) * splits; };
-  if (!s.out_f32 && splits == 1 && ((mt + 1) / 2) * ((s.n + 255) / 256) >= dev.sm_count / 2) return 512;
+  // a pair tile is 256 rows tall: groups much shorter than that would leave half of every
+  // pair idle, and such shapes are bound by streaming the weights anyway
+  const bool tall_groups = s.avg_group_rows >= 384;
+  if (!s.out_f32 && splits == 1 && tall_groups &&
+      ((mt + 1) / 2) * ((s.n + 255) / 256) >= dev.sm_count / 2)
+    return 512;
   if (tasks(256) >= dev.sm_count * 2 / 3) return 256;
   if (tasks(128) >= dev.sm_count * 3 / 4) return 128;
   return 64;
@@ -267,6 +273,7 @@ int gemm_dense(int groups, int m, int n, int k, const void* a, const void* b, co
   s.num_splits = 1;
   s.expected_m_tiles = groups * ((m + kBlockM - 1) / kBlockM);
   s.exact_m_tiles = true;
+  s.avg_group_rows = m;
   return launch_gemm(s, stream, env_tile_n());
 }
 
@@ -302,6 +309,7 @@ int gemm_splitk(int m, int n, int k, int split_k, const void* a, const void* b, 
   s.num_splits = split_k;
   s.expected_m_tiles = (m + kBlockM - 1) / kBlockM;
   s.exact_m_tiles = true;
+  s.avg_group_rows = m;
   int status = launch_gemm(s, stream, env_tile_n());
   if (status != B200_NVFP4_SUCCESS) return status;
   const DeviceInfo& dev = current_device_info();
@@ -357,6 +365,7 @@ int gemm_grouped(void* y, const void* x, const void* w, const void* seqlens,
   if (est < 1) est = 1;
   s.expected_m_tiles = static_cast<int>(est);
   s.exact_m_tiles = false;
+  s.avg_group_rows = avg;
   return launch_gemm(s, stream, env_tile_n());
 }
 
