@@ -81,6 +81,24 @@ B200_NVFP4_API int b200_nvfp4_gemm_splitk(int m, int n, int k, int split_k, cons
                                           void* c_f16, void* workspace, size_t workspace_bytes,
                                           b200_stream_t stream);
 
+/* Split-K GEMM for callers that cannot hand over a workspace and must not allocate one: a
+ * plugin hook that receives only operand pointers and a stream, a runtime whose memory plan
+ * is frozen, a serving loop that may not touch the device allocator (an allocation can
+ * synchronise the device). Same arithmetic and result as b200_nvfp4_gemm_splitk; the FP32
+ * partial sums go to a fixed 16 MiB array in the library's device data segment, so the call
+ * allocates nothing. No counterpart in the reference.
+ *   - split_k * M * N must not exceed b200_nvfp4_gemm_splitk_static_max_elements() (4 Mi);
+ *     beyond it the call returns B200_NVFP4_INSUFFICIENT_WORKSPACE and launches nothing.
+ *   - one array per device: calls that overlap in time on the same device race on it;
+ *     keep them on one stream or order them with events.
+ *   - the first call on each device looks the array's address up on the host; make it before
+ *     starting any stream capture.
+ *   - the array needs no clearing between calls. */
+B200_NVFP4_API size_t b200_nvfp4_gemm_splitk_static_max_elements(void);
+B200_NVFP4_API int b200_nvfp4_gemm_splitk_static(int m, int n, int k, int split_k, const void* a,
+                                                 const void* b, const void* sfa, const void* sfb,
+                                                 void* c_f16, b200_stream_t stream);
+
 /* nvfp4_gemm_sm120 (src/gemm/gemm_dispatch.cu:63-90): default dispatcher. */
 B200_NVFP4_API int b200_nvfp4_gemm_auto(int m, int n, int k, const void* a, const void* b,
                                         const void* sfa, const void* sfb, void* c_f16,
