@@ -226,6 +226,33 @@ B200_NVFP4_API int b200_nvfp4_expert_moe(void* output, const void* input, const 
                                          int num_expert_local, int grouped_scale_m_pad,
                                          b200_stream_t stream);
 
+/* Expert-parallel hand-off (no counterpart in the reference library; its hand-off benchmark
+ * benchmarks/integration/benchmark_deepep_handoff.py:356-364 ships one BF16 row per
+ * (token, expert) with torch ops). A token is sent once to each rank that owns one of its
+ * experts, as a wire record
+ *   [payload H/2 | UE4M3 scales H/16 in k-block order | ids k x int32 | weights k x float]
+ * padded to 16 bytes; hidden_size % 64 == 0.
+ *   ep_record_bytes   size of one record.
+ *   ep_dest_ranks     dest[t, r] = r if token t has an expert in [r*per_rank, (r+1)*per_rank)
+ *                     else -1 (int32 [T, world]); b200_nvfp4_moe_route over it with `world`
+ *                     groups gives the rank-major send rows and per-rank counts.
+ *   ep_pack_rows      quantises each token row (FP16 / BF16) to NVFP4 once and writes its record
+ *                     at every send_pos[t, r] >= 0.
+ *   ep_unpack_rows    received records -> packed [rows, H/2], one scale region of
+ *                     align128(rows) rows in the block-scaled layout, ids and weights [rows, k]:
+ *                     the inputs of b200_nvfp4_fused_moe with rank_ep set. */
+B200_NVFP4_API size_t b200_nvfp4_ep_record_bytes(int hidden_size, int num_topk);
+B200_NVFP4_API int b200_nvfp4_ep_dest_ranks(const void* topk_ids, void* dest, int num_tokens,
+                                            int num_topk, int experts_per_rank, int world,
+                                            b200_stream_t stream);
+B200_NVFP4_API int b200_nvfp4_ep_pack_rows(void* records, const void* x, const void* topk_ids,
+                                           const void* topk_weights, const void* send_pos,
+                                           int num_tokens, int hidden_size, int num_topk, int world,
+                                           int input_is_bf16, b200_stream_t stream);
+B200_NVFP4_API int b200_nvfp4_ep_unpack_rows(void* x_packed, void* x_scale, void* topk_ids,
+                                             void* topk_weights, const void* records, int rows,
+                                             int hidden_size, int num_topk, b200_stream_t stream);
+
 /* Reads and clears the device word in which a kernel records a timed-out wait (every wait
  * inside the kernels is bounded). SYNCHRONISES the device. *code receives 0 when nothing
  * was recorded. No counterpart in the reference. */

@@ -4,22 +4,26 @@ Rank r owns the contiguous expert interval [r*E/W, (r+1)*E/W) - the convention o
 reference's rank_ep / num_expert_local arguments (src/fused_moe/count_and_gather.cu:106-107).
 The exchange pattern follows the reference's only multi-GPU code, the 2-GPU hand-off benchmark
 benchmarks/integration/benchmark_deepep_handoff.py (:55-58 counts, :356-364 dispatch,
-:435-448 combine): one all-to-all of per-expert counts, one all-to-all of token rows each
-way, with `expert_moe` as the compute between them. What differs from that script:
+:435-448 combine): an all-to-all of counts, an all-to-all of token rows each way, with the
+fused MoE as the compute between them. What differs from that script:
 
-  * routing, the row scatter / gather and the weighted combine run in this library's CUDA
-    kernels (b200_nvfp4_moe_route / _scatter_rows / _gather_rows / _reduce);
-  * received rows are quantised to NVFP4 and permuted to expert-major order in one kernel
-    (b200_nvfp4_moe_quantize_expert_gather) instead of an index_select plus a quantise;
-  * route weights are applied once, in FP32, by the combine kernel on the source rank (the
-    script multiplies on the expert rank in BF16 and index_adds in FP32).
+  * a token travels ONCE to each rank that owns at least one of its experts (not once per
+    expert), already quantised to NVFP4 and with its expert ids and route weights in the same
+    wire record (4096 bytes for H = 7168, top-8, against 8 x 14336 bytes of BF16 rows);
+  * the receiving rank runs the whole routed pipeline (`fused_moe` with rank_ep set: local
+    routing, both grouped GEMMs, SiLU * up + requantisation, route-weighted sum over the local
+    experts) and returns ONE partial row per received token;
+  * the source rank adds the partial rows of a token in ascending rank order in FP32.
 
+Packing, unpacking, routing and the final sum are this library's CUDA kernels
+(b200_nvfp4_ep_dest_ranks / _ep_pack_rows / _ep_unpack_rows, b200_nvfp4_moe_route / _reduce).
 torch.distributed (NCCL over NVLink / NVSwitch, gloo on CPU) is the transport; the split sizes
-of the row exchanges are read back to the host once per call, as in the reference script.
+of the row exchanges are read back to the host once per call, as in the reference script. All
+kernels read and write local HBM only.
 
-The compute steps go through a small backend object so that the host logic (maps, splits,
-ordering) can be exercised on CPU ranks with a checker backend supplied by the tests; the
-default backend calls the C ABI and needs a CUDA device.
+The compute steps go through a small backend object so that the host logic (splits, ordering,
+the two exchanges) can be exercised on CPU ranks with a checker backend supplied by the tests;
+the default backend calls the C ABI and needs a CUDA device.
 """
 from __future__ import annotations
 
@@ -32,6 +36,11 @@ from . import _lib
 from .ops import scale_k_padded
 
 
+def record_bytes(hidden: int, topk: int) -> int:
+    """Bytes of one wire record: payload, k-block-ordered scales, ids, weights, 16-byte padded."""
+    return (hidden // 2 + hidden // 16 + 8 * topk + 15) // 16 * 16
+
+
 class CudaBackend:
     """The product path: every step is a call into the C ABI on torch's current stream."""
 
@@ -42,56 +51,51 @@ class CudaBackend:
     def _stream(t: torch.Tensor) -> int:
         return torch.cuda.current_stream(t.device).cuda_stream
 
-    def route(self, topk_ids, num_experts):
+    def dest_ranks(self, topk_ids, experts_per_rank, world):
         t, k = topk_ids.shape
-        dev = topk_ids.device
+        dest = torch.empty((t, world), dtype=torch.int32, device=topk_ids.device)
+        _lib.check(self.L.b200_nvfp4_ep_dest_ranks(topk_ids.data_ptr(), dest.data_ptr(), t, k, experts_per_rank,
+                                                   world, self._stream(topk_ids)), "ep_dest_ranks")
+        return dest
+
+    def route(self, ids, num_groups):
+        t, k = ids.shape
+        dev = ids.device
         pos = torch.empty((t, k), dtype=torch.int32, device=dev)
-        seqlens = torch.empty(num_experts, dtype=torch.int32, device=dev)
-        cu = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
-        _lib.check(self.L.b200_nvfp4_moe_route(topk_ids.data_ptr(), pos.data_ptr(), seqlens.data_ptr(),
-                                               cu.data_ptr(), t, k, num_experts, 0, self._stream(topk_ids)),
+        seqlens = torch.empty(num_groups, dtype=torch.int32, device=dev)
+        cu = torch.empty(num_groups + 1, dtype=torch.int32, device=dev)
+        _lib.check(self.L.b200_nvfp4_moe_route(ids.data_ptr(), pos.data_ptr(), seqlens.data_ptr(),
+                                               cu.data_ptr(), t, k, num_groups, 0, self._stream(ids)),
                    "moe_route")
         return pos, seqlens, cu
 
-    def scatter_rows(self, src, pos, rows_out):
-        out = torch.empty((rows_out, src.shape[1]), dtype=src.dtype, device=src.device)
-        _lib.check(self.L.b200_nvfp4_moe_scatter_rows(out.data_ptr(), src.data_ptr(), pos.data_ptr(), pos.numel(),
-                                                      pos.shape[1], src.shape[1] * src.element_size(),
-                                                      self._stream(src)), "moe_scatter_rows")
-        return out
+    def pack_rows(self, x, topk_ids, topk_weights, send_pos, rows_out):
+        t, hidden = x.shape
+        k, world = topk_ids.shape[1], send_pos.shape[1]
+        rb = self.L.b200_nvfp4_ep_record_bytes(hidden, k)
+        rec = torch.empty((rows_out, rb), dtype=torch.uint8, device=x.device)
+        _lib.check(self.L.b200_nvfp4_ep_pack_rows(rec.data_ptr(), x.data_ptr(), topk_ids.data_ptr(),
+                                                  topk_weights.data_ptr(), send_pos.data_ptr(), t, hidden, k, world,
+                                                  int(x.dtype == torch.bfloat16), self._stream(x)), "ep_pack_rows")
+        return rec
 
-    def gather_rows(self, src, index, rows_out):
-        out = torch.empty((rows_out, src.shape[1]), dtype=src.dtype, device=src.device)
-        if rows_out:
-            _lib.check(self.L.b200_nvfp4_moe_gather_rows(out.data_ptr(), src.data_ptr(), index.data_ptr(), rows_out,
-                                                         src.shape[1] * src.element_size(), self._stream(src)),
-                       "moe_gather_rows")
-        return out
+    def unpack_rows(self, records, hidden, topk):
+        rows = records.shape[0]
+        dev = records.device
+        m_pad = max(128, (rows + 127) // 128 * 128)
+        xq = torch.empty((rows, hidden // 2), dtype=torch.uint8, device=dev)
+        xs = torch.empty(m_pad * scale_k_padded(hidden), dtype=torch.uint8, device=dev)
+        ids = torch.empty((rows, topk), dtype=torch.int32, device=dev)
+        wts = torch.empty((rows, topk), dtype=torch.float32, device=dev)
+        _lib.check(self.L.b200_nvfp4_ep_unpack_rows(xq.data_ptr(), xs.data_ptr(), ids.data_ptr(), wts.data_ptr(),
+                                                    records.data_ptr(), rows, hidden, topk, self._stream(records)),
+                   "ep_unpack_rows")
+        return xq, xs, ids, wts
 
-    def quantize_gather(self, rows, row_map, seqlens, cu_seqlens, m_pad):
-        r, hidden = row_map.numel(), rows.shape[1]
-        e = seqlens.numel()
-        packed = torch.empty((max(r, 1), hidden // 2), dtype=torch.uint8, device=rows.device)
-        scales = torch.empty((e, m_pad * scale_k_padded(hidden)), dtype=torch.uint8, device=rows.device)
-        if r:
-            _lib.check(self.L.b200_nvfp4_moe_quantize_expert_gather(
-                packed.data_ptr(), scales.data_ptr(), rows.data_ptr(), row_map.data_ptr(), seqlens.data_ptr(),
-                cu_seqlens.data_ptr(), e, r, hidden, m_pad, int(rows.dtype == torch.bfloat16), 0,
-                self._stream(rows)), "moe_quantize_expert_gather")
-        return packed, scales
-
-    def expert_moe(self, packed, scales, gate_up_w, gate_up_ws, down_w, down_ws, seqlens, cu_seqlens, rows, m_pad):
-        hidden = packed.shape[1] * 2
-        e, inter = gate_up_w.shape[0], gate_up_w.shape[1] // 2
-        out = torch.empty((max(rows, 1), hidden), dtype=torch.float16, device=packed.device)
-        if rows:
-            need = self.L.b200_nvfp4_expert_moe_workspace_bytes(rows, hidden, inter, e, m_pad)
-            ws = torch.empty(need, dtype=torch.uint8, device=packed.device)
-            _lib.check(self.L.b200_nvfp4_expert_moe(
-                out.data_ptr(), packed.data_ptr(), scales.data_ptr(), gate_up_w.data_ptr(), gate_up_ws.data_ptr(),
-                down_w.data_ptr(), down_ws.data_ptr(), seqlens.data_ptr(), cu_seqlens.data_ptr(), ws.data_ptr(), need,
-                rows, hidden, inter, e, m_pad, self._stream(packed)), "expert_moe")
-        return out
+    def local_moe(self, xq, xs, ids, wts, gate_up_w, gate_up_ws, down_w, down_ws, rank, num_experts_total):
+        from . import ops
+        return ops.fused_moe(xq, xs, gate_up_w, gate_up_ws, down_w, down_ws, ids, wts, ep_rank=rank,
+                             num_experts=num_experts_total)
 
     def reduce(self, rows, pos, weights, out_bf16):
         t, k = pos.shape
@@ -100,35 +104,6 @@ class CudaBackend:
         _lib.check(self.L.b200_nvfp4_moe_reduce(out.data_ptr(), rows.data_ptr(), pos.data_ptr(), weights.data_ptr(),
                                                 None, t, hidden, k, int(out_bf16), self._stream(rows)), "moe_reduce")
         return out
-
-
-def expert_major_maps(counts: torch.Tensor, total: int):
-    """counts[s, e] = rows rank s sent for local expert e (int64, on the compute device).
-
-    The receive buffer is source-major (all of rank 0's rows, sorted by expert, then rank 1's
-    ...). Returns (seqlens[e], cu_seqlens[e+1], row_map, inv_map): row_map[i] = receive-buffer
-    row of expert-major row i (experts ascending, sources ascending inside an expert, send order
-    inside a source) and inv_map its inverse.
-    """
-    w, e = counts.shape
-    dev = counts.device
-    seqlens = counts.sum(0)
-    cu = torch.zeros(e + 1, dtype=torch.int64, device=dev)
-    cu[1:] = torch.cumsum(seqlens, 0)
-    src_base = torch.zeros(w, dtype=torch.int64, device=dev)
-    src_base[1:] = torch.cumsum(counts.sum(1), 0)[:-1]
-    recv_start = src_base[:, None] + torch.cumsum(counts, 1) - counts            # [w, e]
-    em_start = cu[:-1][None, :] + torch.cumsum(counts, 0) - counts               # [w, e]
-    # blocks in expert-major order: (e, s)
-    lens = counts.t().reshape(-1)
-    recv_s = recv_start.t().reshape(-1)
-    em_s = em_start.t().reshape(-1)
-    block = torch.repeat_interleave(torch.arange(w * e, device=dev), lens, output_size=total)
-    idx = torch.arange(total, device=dev)
-    row_map = (recv_s[block] + (idx - em_s[block])).to(torch.int32)
-    inv_map = torch.empty(total, dtype=torch.int32, device=dev)
-    inv_map[row_map.long()] = idx.to(torch.int32)
-    return seqlens.to(torch.int32), cu.to(torch.int32), row_map, inv_map
 
 
 class ExpertParallelMoE:
@@ -152,6 +127,7 @@ class ExpertParallelMoE:
             raise ValueError("num_experts_total must equal world_size * local experts")
         self.backend = backend if backend is not None else CudaBackend()
         self.last_bytes = {"dispatch": 0, "combine": 0}
+        self._ones = None
 
     def _all_to_all_rows(self, send, send_splits, recv_splits):
         recv = torch.empty((sum(recv_splits), send.shape[1]), dtype=send.dtype, device=send.device)
@@ -163,35 +139,36 @@ class ExpertParallelMoE:
 
     @torch.no_grad()
     def forward(self, x, topk_ids, topk_weights, out_bf16: bool = True):
-        w, e_local, be = self.world, self.e_local, self.backend
-        t, k = topk_ids.shape
-        total = t * k
-        # 1. expert-major positions over ALL experts = (destination rank, expert, flat index) order
-        pos, seqlens, _ = be.route(topk_ids, self.num_experts_total)
-        send_counts = seqlens.view(w, e_local).to(torch.int64)
-        # 2. per-expert counts to every destination rank
+        w, be = self.world, self.backend
+        t, hidden = x.shape
+        k = topk_ids.shape[1]
+        # 1. which ranks does each token visit, and at which row of the rank-major send buffer
+        dest = be.dest_ranks(topk_ids, self.e_local, w)
+        send_pos, send_counts, _ = be.route(dest, w)
+        # 2. row counts to every destination; quantise + pack while the host waits for them
         recv_counts = torch.empty_like(send_counts)
         if w == 1:
             recv_counts.copy_(send_counts)
         else:
             dist.all_to_all_single(recv_counts, send_counts, group=self.group)
-        host = torch.cat((send_counts.sum(1), recv_counts.reshape(-1))).cpu()   # the one host read-back
-        send_splits = host[:w].tolist()
-        recv_host = host[w:].view(w, e_local)
-        recv_splits = recv_host.sum(1).tolist()
-        # 3. dispatch: token rows in send order, then the exchange
-        send_rows = be.scatter_rows(x, pos, total)
-        recv_rows = self._all_to_all_rows(send_rows, send_splits, recv_splits)
-        self.last_bytes["dispatch"] = (total - send_splits[self.rank]) * x.shape[1] * x.element_size()
-        # 4. local experts: permute + quantise, gate/up GEMM, SiLU*up + quantise, down GEMM
-        rows = int(sum(recv_splits))
-        seq_l, cu_l, row_map, inv_map = expert_major_maps(recv_counts, rows)
-        max_rows = int(recv_host.sum(0).max()) if rows else 0
-        m_pad = max(128, (max_rows + 127) // 128 * 128)
-        packed, scales = be.quantize_gather(recv_rows, row_map, seq_l, cu_l, m_pad)
-        y = be.expert_moe(packed, scales, self.gw, self.gws, self.dw, self.dws, seq_l, cu_l, rows, m_pad)
-        # 5. combine: rows back in receive order, the exchange, weighted top-k sum at the source
-        back = be.gather_rows(y, inv_map, rows)
-        ret = self._all_to_all_rows(back, recv_splits, send_splits)
-        self.last_bytes["combine"] = (rows - recv_splits[self.rank]) * y.shape[1] * y.element_size()
-        return be.reduce(ret, pos, topk_weights, out_bf16)
+        records = be.pack_rows(x, topk_ids, topk_weights, send_pos, t * w)
+        host = torch.cat((send_counts, recv_counts)).cpu()          # the one host read-back
+        send_splits, recv_splits = host[:w].tolist(), host[w:].tolist()
+        sent = int(sum(send_splits))
+        # 3. dispatch
+        got = self._all_to_all_rows(records[:sent], send_splits, recv_splits)
+        self.last_bytes["dispatch"] = (sent - send_splits[self.rank]) * records.shape[1]
+        rows = got.shape[0]
+        # 4. the routed pipeline over this rank's experts: one partial row per received token
+        if rows:
+            xq, xs, ids, wts = be.unpack_rows(got, hidden, k)
+            part = be.local_moe(xq, xs, ids, wts, self.gw, self.gws, self.dw, self.dws, self.rank,
+                                self.num_experts_total)
+        else:
+            part = torch.empty((0, hidden), dtype=torch.float16, device=x.device)
+        # 5. combine: partial rows back to their sources, summed there in ascending rank order
+        ret = self._all_to_all_rows(part, recv_splits, send_splits)
+        self.last_bytes["combine"] = (rows - recv_splits[self.rank]) * hidden * 2
+        if self._ones is None or self._ones.shape != (t, w) or self._ones.device != x.device:
+            self._ones = torch.ones((t, w), dtype=torch.float32, device=x.device)
+        return be.reduce(ret, send_pos, self._ones, out_bf16)

@@ -1,0 +1,82 @@
+"""GPU tests of the expert-parallel hand-off kernels (destination ranks, wire-record pack /
+unpack) and of the expert-parallel layer on one rank, through the C ABI, against the numpy /
+oracle checker backend used by the CPU multi-rank test. Integer and byte outputs bit-exact;
+the layer output within the GEMM gate."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import check_gemm_parity, randn_quantized, topk_routing
+from test_ep_gloo import OracleBackend, expected_ep_output
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def backend():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from sm120_nvfp4_b200 import _lib
+    from sm120_nvfp4_b200.ep import CudaBackend
+    _lib.lib()
+    yield CudaBackend()
+    assert _lib.device_error() == 0
+
+
+def _bf16_rows(tokens, hidden, seed):
+    rng = np.random.default_rng(seed)
+    x = torch.from_numpy(rng.standard_normal((tokens, hidden), dtype=np.float32)).to(torch.bfloat16)
+    return x
+
+
+@pytest.mark.parametrize("tokens,experts,topk,world,hidden", [(37, 8, 3, 2, 128), (1500, 64, 8, 8, 448),
+                                                               (4096, 256, 8, 4, 7168)])
+def test_pack_and_unpack_match_checker(backend, tokens, experts, topk, world, hidden):
+    chk = OracleBackend()
+    ids, w = topk_routing(tokens, experts, topk, 77)
+    x = _bf16_rows(tokens, hidden, 5)
+    ids_t, w_t = torch.from_numpy(ids), torch.from_numpy(w)
+    per_rank = experts // world
+    dest = backend.dest_ranks(ids_t.cuda(), per_rank, world)
+    want_dest = chk.dest_ranks(ids_t, per_rank, world)
+    assert torch.equal(dest.cpu(), want_dest)
+    pos, counts, cu = backend.route(dest, world)
+    want_pos, want_counts, want_cu = chk.route(want_dest, world)
+    assert torch.equal(pos.cpu(), want_pos) and torch.equal(counts.cpu(), want_counts) and torch.equal(cu.cpu(), want_cu)
+    sent = int(want_cu[-1])
+    rec = backend.pack_rows(x.cuda(), ids_t.cuda(), w_t.cuda(), pos, tokens * world)
+    want_rec = chk.pack_rows(x, ids_t, w_t, want_pos, tokens * world)
+    body = hidden // 2 + hidden // 16 + 8 * topk
+    assert torch.equal(rec[:sent, :body].cpu(), want_rec[:sent, :body])
+    # the receiving side, fed with the sender's records as they are
+    xq, xs, rid, rw = backend.unpack_rows(rec[:sent].contiguous(), hidden, topk)
+    wq, ws, wid, ww = chk.unpack_rows(want_rec[:sent], hidden, topk)
+    assert torch.equal(xq.cpu(), wq) and torch.equal(rid.cpu(), wid) and torch.equal(rw.cpu(), ww)
+    # scale bytes of live rows (the padding rows of the region are not written)
+    nkb = hidden // 16
+    r = np.repeat(np.arange(sent, dtype=np.int32), nkb)
+    kb = np.tile(np.arange(nkb, dtype=np.int32), sent)
+    off = oracle.sf_offsets(r, kb, hidden)
+    np.testing.assert_array_equal(xs.cpu().numpy()[off], ws.numpy()[off])
+
+
+def test_layer_on_one_rank_matches_oracle(backend):
+    from sm120_nvfp4_b200.ep import ExpertParallelMoE
+    experts, hidden, inter, topk, tokens = 8, 256, 128, 3, 200
+    gw = np.empty((experts, 2 * inter, hidden // 2), np.uint8)
+    gws = np.empty((experts, oracle.scale_region_bytes(2 * inter, hidden)), np.uint8)
+    dw = np.empty((experts, hidden, inter // 2), np.uint8)
+    dws = np.empty((experts, oracle.scale_region_bytes(hidden, inter)), np.uint8)
+    for e in range(experts):
+        gw[e], gws[e] = randn_quantized(2 * inter, hidden, 10 + 2 * e, 0.5)
+        dw[e], dws[e] = randn_quantized(hidden, inter, 11 + 2 * e, 0.5)
+    x = _bf16_rows(tokens, hidden, 9)
+    ids, w = topk_routing(tokens, experts, topk, 31)
+    layer = ExpertParallelMoE(torch.from_numpy(gw).cuda(), torch.from_numpy(gws).cuda(), torch.from_numpy(dw).cuda(),
+                              torch.from_numpy(dws).cuda(), experts, backend=backend)
+    out = layer.forward(x.cuda(), torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), out_bf16=False)
+    torch.cuda.synchronize()
+    xb = x.view(torch.int16).numpy().view(np.uint16)
+    want = expected_ep_output(xb, ids, w, gw, gws, dw, dws, 1)
+    check_gemm_parity(out.cpu().numpy(), want.astype(np.float32))
