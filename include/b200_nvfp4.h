@@ -267,7 +267,7 @@ B200_NVFP4_API int b200_nvfp4_set_tile_n(int tile_n);
 
 /* Debug aid: copies the first `count` (<= 2048) 64-bit time stamps the GEMM kernel recorded
  * when the environment variable B200_NVFP4_DEBUG has bit 64 set (first two CTAs, first 64
- * pipeline iterations; layout ((cta*4 + role)*64 + iter)*2 + {before, after}; SM clock
+ * pipeline iterations; layout ((cta*8 + role)*64 + iter)*2 + {before, after}; SM clock
  * cycles). SYNCHRONISES. No counterpart in the reference. */
 B200_NVFP4_API int b200_nvfp4_debug_trace(unsigned long long* out, int count);
 

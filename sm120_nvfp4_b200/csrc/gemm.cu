@@ -86,7 +86,19 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
     return B200_NVFP4_CUDA_ERROR;
   }
 
+  // Output map for the TMA-store epilogue: boxes of 32 rows x 128 bytes. Split-K slices are
+  // stacked along the rows. Tiles of 64 columns and matrices narrower than one box use plain
+  // stores only.
+  CUtensorMap tmap_out = tmap_a;
+  const int box_cols = F32 ? 32 : 64;
+  const long long out_rows = static_cast<long long>(s.a_rows_total) * (s.num_splits > 1 ? s.num_splits : 1);
+  const bool tma_store = BN >= 128 && s.n >= box_cols && out_rows < 0x7fffffffLL &&
+                         encode_tmap_2d_out(&tmap_out, s.out, static_cast<uint64_t>(out_rows),
+                                            static_cast<uint64_t>(s.n), F32, 32, box_cols);
+
   GemmParams p;
+  p.tma_store = tma_store ? 1 : 0;
+  p.out_rows_per_split = s.num_splits > 1 ? s.a_rows_total : 0;
   p.num_groups = s.num_groups;
   p.n = s.n;
   p.k = s.k;
@@ -156,7 +168,7 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   attrs[0].val.clusterDim.z = 1;
   config.attrs = attrs;
   config.numAttrs = 1;
-  const cudaError_t launched = cudaLaunchKernelEx(&config, kernel, tmap_a, tmap_b, p);
+  const cudaError_t launched = cudaLaunchKernelEx(&config, kernel, tmap_a, tmap_b, tmap_out, p);
   count_launch();
   return launched == cudaSuccess && cudaPeekAtLastError() == cudaSuccess ? B200_NVFP4_SUCCESS
                                                                           : B200_NVFP4_CUDA_ERROR;

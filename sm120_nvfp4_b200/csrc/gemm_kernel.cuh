@@ -87,6 +87,8 @@ struct GemmParams {
   int* error;                 // device word that receives a non-zero code on a timed-out wait
   int num_stages;             // depth of the operand ring in shared memory (<= kMaxStages)
   int num_sf_slots;           // depth of the scale-atom ring in shared memory (<= kMaxSfSlots)
+  int tma_store;              // 1: the output tensor map is valid, full 32-row slabs go out by TMA store
+  int out_rows_per_split;     // rows between split-K slices in the output tensor map (M), 0 without split
   int debug;                  // bit 64: record time stamps into `trace` (0 in production)
   unsigned long long* trace;  // optional time-stamp buffer (debug bit 64), else nullptr
 };
@@ -104,9 +106,10 @@ struct GemmCfg {
   static constexpr int kSfbGroups = (BN + 127) / 128;       // 128-row scale tiles per B tile
   static constexpr int kSfbColsPerMma = 4 * kSfbGroups;     // TMEM columns of SFB per MMA
   static constexpr int kAccStages = BN <= 128 ? 2 : 1;
-  // Tensor memory: accumulator stage(s) first, then one scale-factor buffer per shared-memory
-  // stage, so the scale copies of a k-stage can be issued (by their own warp) while the MMAs
-  // of earlier stages are still running.
+  // Tensor memory: accumulator stage(s) first, then a ring of scale-factor buffers, one per
+  // k-stage in flight, so the scale copies of a k-stage can be issued (by their own warps)
+  // while the MMAs of earlier stages are still running. The ring is as deep as the columns
+  // allow, but never deeper than the operand ring (kernel: sf_depth).
   static constexpr int kSfColsPerBuf = 16 + 4 * kSfbColsPerMma;   // 4 MMAs: SFA 4x4, SFB 4xN/32
   static constexpr int kSfBase = kAccStages * BN;
   static constexpr int kMaxSfBufs = (512 - kSfBase) / kSfColsPerBuf;
@@ -117,19 +120,23 @@ struct GemmCfg {
   static constexpr int kSfbBytes = kSfbGroups * 4 * kAtomBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;       // one stage of the operand ring
   static constexpr int kSfSlotBytes = kSfaBytes + kSfbBytes;  // one slot of the scale-atom ring
+  // Output staging for TMA stores: 32 rows x 128 bytes per epilogue warp. Tiles of 64 columns
+  // give a warp only 32 columns (64 bytes of FP16 per row) and keep the direct-store epilogue.
+  static constexpr int kStagingWarpBytes = 32 * 128;
+  static constexpr int kStagingBytes = BN >= 128 ? kEpilogueWarps * kStagingWarpBytes : 0;
 
-  // Shared memory: [operand stages][scale slots][barriers][group tables]; +1024 slack to align
+  // Shared memory: [operand stages][output staging][scale slots][barriers][group tables]; +1024 slack to align
   // the base. The scale atoms have a ring of their own: a slot is free again as soon as the
   // movers have read it into registers, so scale loads (small, long-latency bulk copies) run
   // well ahead of the operand ring instead of waiting for MMAs to release a stage.
   static constexpr int fixed_bytes(int num_groups) {
-    return 1024 + kBarrierBytes + 3 * (num_groups + 1) * 4;
+    return 1024 + kBarrierBytes + 3 * (num_groups + 1) * 4 + kStagingBytes;
   }
+  static constexpr int kMinSfSlots = 4;
   static constexpr int stages_for(int num_groups) {
-    // keep room for at least as many scale slots as operand stages
-    int s = (kSmemBudget - fixed_bytes(num_groups)) / (kStageBytes + kSfSlotBytes);
-    s = s > kMaxStages ? kMaxStages : s;
-    return s > kMaxSfBufs ? kMaxSfBufs : s;
+    // as many operand stages as fit beside a minimum of scale slots
+    int s = (kSmemBudget - fixed_bytes(num_groups) - kMinSfSlots * kSfSlotBytes) / kStageBytes;
+    return s > kMaxStages ? kMaxStages : s;
   }
   static constexpr int sf_slots_for(int num_groups) {
     int n = (kSmemBudget - fixed_bytes(num_groups) - stages_for(num_groups) * kStageBytes) / kSfSlotBytes;
@@ -172,11 +179,11 @@ __device__ __forceinline__ TileCoord decode_tile(int task, int total_mt, int n_t
   return t;
 }
 
-// Debug time stamps: trace[((cta * 4 + role) * 64 + iter) * 2 + which] = SM clock counter.
+// Debug time stamps: trace[((cta * 8 + role) * 64 + iter) * 2 + which] = SM clock counter.
 __device__ __forceinline__ void trace_stamp(const GemmParams& p, int role, int iter, int which) {
   if ((p.debug & 64) && p.trace != nullptr && blockIdx.x < 2 && iter < 64) {
     const unsigned long long t = static_cast<unsigned long long>(clock64());
-    p.trace[((blockIdx.x * 4 + role) * 64 + iter) * 2 + which] = t;
+    p.trace[((blockIdx.x * 8 + role) * 64 + iter) * 2 + which] = t;
   }
 }
 
@@ -188,19 +195,25 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 template <int BN, bool kOutF32, bool kTwoCta>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                  const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+                  const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
   using Cfg = GemmCfg<BN, kTwoCta>;
   constexpr int kCtas = Cfg::kCtas;
   constexpr int kAccStages = Cfg::kAccStages;
   constexpr int kTileM = Cfg::kTileM;
   const int kStages = p.num_stages;
+  // k-stages whose scales may sit in tensor memory at once. Not more than operand stages: a
+  // mover that ran further ahead would arrive on a stage's `full` barrier before the stage's
+  // previous use had completed.
+  const int sf_depth = Cfg::kMaxSfBufs < kStages ? Cfg::kMaxSfBufs : kStages;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* stage_base = smem;
   const int kSfSlots = p.num_sf_slots;
-  uint8_t* sf_base = smem + kStages * Cfg::kStageBytes;
+  uint8_t* staging_base = smem + kStages * Cfg::kStageBytes;   // 1024-byte aligned: stages are multiples of 1 KB
+  uint8_t* sf_base = staging_base + Cfg::kStagingBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(sf_base + kSfSlots * Cfg::kSfSlotBytes);
   // full:      the stage is ready for the MMAs: its A / B tiles landed in shared memory and
   //            its scales are in tensor memory (pair: in both CTAs; lives in the first CTA).
@@ -254,6 +267,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
+    if (p.tma_store) ptx::prefetch_tensormap(&tmap_out);
   }
   __syncthreads();
   if (warp == kWarpLoadA) {  // exclusive scan of the per-group tile counts, 32 groups at a time
@@ -325,12 +339,14 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int ks_begin = (k_stages * t.split) / p.num_splits;
         const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
         for (int ks = ks_begin; ks < ks_end; ++ks) {
-          if (is_a && lane == 0) trace_stamp(p, 0, iter, 0);
+          if (lane == 0) trace_stamp(p, is_a ? 0 : 4, iter, 0);
           if (!peeked && !ptx::mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, 1)) { ok = false; break; }
-          if (is_a && lane == 0) trace_stamp(p, 0, iter, 1);
+          if (lane == 0) trace_stamp(p, is_a ? 0 : 4, iter, 1);
           ++iter;
           uint8_t* dst = stage_base + stage * Cfg::kStageBytes + (is_a ? 0 : Cfg::kABytes);
-          if (ptx::elect_one()) {
+          if (p.debug & 2) {   // experiment: no operand traffic, barriers only
+            if (ptx::elect_one() && leader) ptx::mbar_arrive(full_bar + stage);
+          } else if (ptx::elect_one()) {
             if constexpr (kTwoCta) {
               if (leader) ptx::mbar_arrive_expect_tx(full_bar + stage, 2 * bytes);
               ptx::tma_load_2d_pair(dst, tmap, ptx::map_to_cta(full_bar + stage, 0), ks * kStageKBytes, row);
@@ -373,7 +389,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           uint8_t* ssfb = ssfa + Cfg::kSfaBytes;
           const int atoms = min(4, kt - ks * 4);
           const uint32_t sf_bytes = static_cast<uint32_t>(atoms) * kAtomBytes;
-          if (ptx::elect_one()) {
+          if (p.debug & 8) {   // experiment: no scale traffic
+            if (ptx::elect_one()) ptx::mbar_arrive(sf_landed_bar + stage);
+          } else if (ptx::elect_one()) {
             ptx::mbar_arrive_expect_tx(sf_landed_bar + stage, sf_bytes * (1 + sfb_groups));
             ptx::bulk_load(ssfa, sfa_tile + static_cast<long long>(ks) * 4 * kAtomBytes, sf_bytes,
                            sf_landed_bar + stage);
@@ -394,7 +412,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (leader) {
       constexpr uint32_t idesc = ptx::make_idesc_nvfp4(kTileM, BN);
       constexpr uint16_t kAllCtas = kTwoCta ? 3 : 1;
-      int stage = 0, acc = 0, iter = 0;
+      int stage = 0, acc = 0, iter = 0, sfbuf = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true, peeked = false;
       for (int task = worker; task < total_tasks && ok; task += num_workers) {
@@ -404,7 +422,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // A tile narrower than 128 columns uses part of a 128-row scale atom: column
         // (n0 % 128) / 32 of the four TMEM columns the atom occupies.
         const uint32_t sfb_sub = BN < 128 ? static_cast<uint32_t>(((t.nt * BN) % 128) / 32) : 0u;
+        if (lane == 0) trace_stamp(p, 7, iter / 32, 0);
         if (!ptx::mbar_wait(acc_empty_bar + acc, acc_phase ^ 1, abort_flag, 2)) break;
+        if (lane == 0) trace_stamp(p, 7, iter / 32, 1);
         ptx::tc_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int ks = ks_begin; ks < ks_end; ++ks) {
@@ -419,14 +439,15 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t a_addr = ptx::smem_u32(stage_base + stage * Cfg::kStageBytes);
           const uint32_t b_addr = a_addr + Cfg::kABytes;
           const int atoms = min(4, kt - ks * 4);
-          const uint32_t sfa_col = tmem_base + Cfg::kSfBase + stage * Cfg::kSfColsPerBuf;
+          const uint32_t sfa_col = tmem_base + Cfg::kSfBase + sfbuf * Cfg::kSfColsPerBuf;
           const uint32_t sfb_col = sfa_col + 16 + sfb_sub;
           const uint64_t a_desc = ptx::make_kmajor_sw128_desc(a_addr);
           const uint64_t b_desc = ptx::make_kmajor_sw128_desc(b_addr);
           const uint32_t accumulate_first = ks > ks_begin ? 1u : 0u;
           if (ptx::elect_one()) {
             // 64 E2M1 values = 32 bytes along K: +2 in the descriptor's 16-byte address field
-            if (atoms == 4) {
+            if (p.debug & 1) {   // experiment: data path only, no MMAs
+            } else if (atoms == 4) {
               ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_desc, b_desc, idesc, sfa_col, sfb_col, accumulate_first);
               ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_desc + 2, b_desc + 2, idesc, sfa_col + 4,
                                        sfb_col + Cfg::kSfbColsPerMma, 1u);
@@ -443,6 +464,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ptx::tc_commit<kCtas>(empty_bar + stage, kAllCtas);
           }
           ++iter;
+          if (++sfbuf == sf_depth) sfbuf = 0;
           stage = next_stage;
           if (stage == 0) phase ^= 1;
         }
@@ -459,8 +481,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // hold the same 16 bytes per lane: row r of an atom lives in lane r % 32, column r / 32).
     // Lane t reads the 16 bytes at offset 16 t of each atom.
     const int q = warp & 3;
-    int stage = 0, slot = 0, iter = 0;
-    uint32_t phase = 0, slot_phase = 0;
+    int stage = 0, slot = 0, iter = 0, sfbuf = 0;
+    int lag_stage = 0, ahead = 0;   // operand stage of the k-stage sf_depth back; k-stages moved so far (saturates)
+    uint32_t lag_phase = 0, slot_phase = 0;
     bool ok = true;
     for (int task = worker; task < total_tasks && ok; task += num_workers) {
       TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
@@ -468,10 +491,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
       for (int ks = ks_begin; ks < ks_end; ++ks) {
         // 1. atoms of this k-stage: shared memory -> registers
-        int go = 1;
-        if (lane == 0) go = ptx::mbar_wait(sf_landed_bar + slot, slot_phase, abort_flag, 5) ? 1 : 0;
-        go = __shfl_sync(0xffffffffu, go, 0);
-        if (!go) { ok = false; break; }
+        // every lane polls (warp-uniform control flow: a single-lane wait costs a vote and a
+        // broadcast per call, several hundred cycles per k-stage in this loop)
+        if (!ptx::mbar_wait(sf_landed_bar + slot, slot_phase, abort_flag, 5)) { ok = false; break; }
         if (q == 0 && lane == 0) trace_stamp(p, 3, iter, 0);
         const uint8_t* ssfa = sf_base + slot * Cfg::kSfSlotBytes + lane * 16;
         const uint8_t* ssfb = ssfa + Cfg::kSfaBytes;
@@ -494,58 +516,81 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             rb[c] = v.x; rb[c + 1] = v.y; rb[c + 2] = v.z; rb[c + 3] = v.w;
           }
         }
-        // 2. registers -> the stage's tensor-memory buffer, once the MMAs that last read that
-        //    buffer are done (same condition that lets the operand loaders refill the stage)
-        if (lane == 0) go = ptx::mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, 6) ? 1 : 0;
-        go = __shfl_sync(0xffffffffu, go, 0);
-        if (!go) { ok = false; break; }
+        // 2. registers -> this k-stage's tensor-memory buffer, once the MMAs of the k-stage that
+        //    used the buffer last (sf_depth k-stages ago) are done: their commit completes a
+        //    phase of that k-stage's `empty` barrier
+        if (ahead < sf_depth) {
+          ++ahead;
+        } else {
+          if (!ptx::mbar_wait(empty_bar + lag_stage, lag_phase, abort_flag, 6)) { ok = false; break; }
+          if (++lag_stage == kStages) { lag_stage = 0; lag_phase ^= 1; }
+        }
         ptx::tc_fence_after_sync();
         const uint32_t sf_taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                                  static_cast<uint32_t>(Cfg::kSfBase + stage * Cfg::kSfColsPerBuf);
+                                  static_cast<uint32_t>(Cfg::kSfBase + sfbuf * Cfg::kSfColsPerBuf);
+        if (!(p.debug & 4)) {   // experiment switch: skip the tensor-memory stores
         ptx::tmem_st_32x32b_x16(sf_taddr, ra);
         if constexpr (Cfg::kSfbGroups == 2) ptx::tmem_st_32x32b_x32(sf_taddr + 16, rb);
         else ptx::tmem_st_32x32b_x16(sf_taddr + 16, rb);
         ptx::tmem_st_wait();
+        }
         ptx::tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) {
+        if (ptx::elect_one()) {
           if (kTwoCta && !leader) ptx::mbar_arrive_remote(full_bar + stage, 0);
           else ptx::mbar_arrive(full_bar + stage);
           // the stores above consumed every lane's registers, so the slot's bytes have
           // certainly been read: hand it back to the scale loader
           ptx::mbar_arrive(sf_free_bar + slot);
-          if (q == 0) trace_stamp(p, 3, iter, 1);
         }
+        if (q == 0 && lane == 0) trace_stamp(p, 3, iter, 1);
         if (++slot == kSfSlots) { slot = 0; slot_phase ^= 1; }
         ++iter;
-        if (++stage == kStages) { stage = 0; phase ^= 1; }
+        if (++sfbuf == sf_depth) sfbuf = 0;
+        if (++stage == kStages) stage = 0;
       }
     }
   } else {
     // ================================ epilogue ===============================
-    // Warp w reads TMEM lanes 32*(w%4).. (a hardware rule) and half of the tile's columns.
-    // Each thread owns one output row: after the accumulator is in registers (and handed
-    // back to the MMA warp) it writes its row segment with 16-byte stores.
+    // Warp w reads TMEM lanes 32*(w%4).. (a hardware rule) and half of the tile's columns;
+    // each thread holds one output row of the warp's 32-row slab.
+    //   * A slab whose 32 rows are all valid leaves through shared memory: every lane writes
+    //     128 bytes of its row into the warp's staging buffer (128-byte swizzle, conflict-free),
+    //     one lane issues a TMA store of the 32 x 128-byte box. The store engine writes whole
+    //     lines; the load/store pipe sees 8 shared-memory stores per lane instead of row-strided
+    //     global stores that would occupy it for thousands of cycles per tile and hold up every
+    //     mbarrier operation of the other warps on the SM.
+    //   * A ragged slab (end of a group, end of the matrix) and 64-column tiles use predicated
+    //     16-byte global stores.
     const int q = warp & 3;
     const int half = (warp - kFirstEpilogueWarp) >> 2;
     constexpr int kWarpCols = BN / 2;                                 // columns per warp
     constexpr int kLdCols = 32;                                       // columns per TMEM load
-    int acc = 0;
+    constexpr bool kCanStage = Cfg::kStagingBytes > 0;
+    uint8_t* stg = staging_base + (warp - kFirstEpilogueWarp) * Cfg::kStagingWarpBytes;
+    const uint32_t stg_row = ptx::smem_u32(stg) + lane * 128;
+    int acc = 0, tile_iter = 0;
     uint32_t acc_phase = 0;
-    for (int task = worker; task < total_tasks; task += num_workers) {
+    for (int task = worker; task < total_tasks; task += num_workers, ++tile_iter) {
       TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
-      const int row_in_tile = static_cast<int>(cta_rank) * kBlockM + q * 32 + lane;
+      const int slab_row = static_cast<int>(cta_rank) * kBlockM + q * 32;   // first row of the slab in the tile
+      const int row_in_tile = slab_row + lane;
       const bool row_ok = t.mt * kTileM + row_in_tile < s_rows[t.g];
+      const bool slab_full = t.mt * kTileM + slab_row + 32 <= s_rows[t.g];
       const long long out_row = static_cast<long long>(s_row0[t.g]) + t.mt * kTileM + row_in_tile;
       const int col0 = t.nt * BN + half * kWarpCols;
       // A k-split that owns no k-stage (more splits than stages) contributes zeros: the
       // accumulator was never written, so its contents are replaced, not scaled.
       const bool empty_split = (k_stages * t.split) / p.num_splits == (k_stages * (t.split + 1)) / p.num_splits;
       const float alpha = p.group_alpha ? p.group_alpha[t.g] : 1.0f;
+      const bool staged = kCanStage && p.tma_store != 0 && slab_full;
+      // row coordinate of the slab in the output tensor map (split-K slices are stacked)
+      const int map_row = s_row0[t.g] + t.mt * kTileM + slab_row + t.split * p.out_rows_per_split;
       int ready = 1;
       if (lane == 0) ready = ptx::mbar_wait(acc_full_bar + acc, acc_phase, abort_flag, 4) ? 1 : 0;
       ready = __shfl_sync(0xffffffffu, ready, 0);
       if (!ready) break;
+      if (warp == kFirstEpilogueWarp && lane == 0) trace_stamp(p, 5, tile_iter, 0);
       ptx::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(acc * BN + half * kWarpCols);
@@ -555,6 +600,25 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (lane == 0) {
           if (kTwoCta && !leader) ptx::mbar_arrive_remote(acc_empty_bar + acc, 0);
           else ptx::mbar_arrive(acc_empty_bar + acc);
+        }
+      };
+      // 128 bytes (eight 16-byte units in w[0..31]) of this lane's row -> staging, then one TMA
+      // store of the slab's box at column `col`.
+      auto stage_and_store = [&](const uint32_t (&w)[32], int col) {
+        if (lane == 0) ptx::bulk_wait_group_read<0>();   // the previous box has left the buffer
+        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const uint32_t addr = stg_row + (static_cast<uint32_t>(u ^ (lane & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * u]),
+                       "r"(w[4 * u + 1]), "r"(w[4 * u + 2]), "r"(w[4 * u + 3])
+                       : "memory");
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::tma_store_2d(&tmap_out, stg, col, map_row);
+          ptx::bulk_commit_group();
         }
       };
 
@@ -567,40 +631,58 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           ptx::tmem_ld_wait();
           if (c == kWarpCols / 32 - 1) release_accumulator();
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            uint4 o;
-            o.x = empty_split ? 0u : __float_as_uint(__uint_as_float(v[4 * i + 0]) * alpha);
-            o.y = empty_split ? 0u : __float_as_uint(__uint_as_float(v[4 * i + 1]) * alpha);
-            o.z = empty_split ? 0u : __float_as_uint(__uint_as_float(v[4 * i + 2]) * alpha);
-            o.w = empty_split ? 0u : __float_as_uint(__uint_as_float(v[4 * i + 3]) * alpha);
-            if (row_ok && col0 + c * 32 + 4 * i < p.n) *reinterpret_cast<uint4*>(dst + c * 32 + 4 * i) = o;
+          for (int i = 0; i < 32; ++i) v[i] = empty_split ? 0u : __float_as_uint(__uint_as_float(v[i]) * alpha);
+          if (staged) {
+            if (col0 + c * 32 < p.n) stage_and_store(v, col0 + c * 32);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              if (row_ok && col0 + c * 32 + 4 * i < p.n)
+                *reinterpret_cast<uint4*>(dst + c * 32 + 4 * i) = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            }
           }
         }
       } else {
-        uint32_t packed[kWarpCols / 2];
+        __half* dst = static_cast<__half*>(p.out) + out_row * p.n + col0;
+        constexpr int kChunkCols = kWarpCols >= 64 ? 64 : kWarpCols;     // columns per pass
+#pragma unroll 1
+        for (int c = 0; c < kWarpCols / kChunkCols; ++c) {
+          uint32_t packed[32];
 #pragma unroll
-        for (int c = 0; c < kWarpCols / kLdCols; ++c) {
-          uint32_t v[kLdCols];
-          ptx::tmem_ld_32x32b_x32(taddr + c * 32, v);
-          ptx::tmem_ld_wait();
+          for (int h = 0; h < kChunkCols / kLdCols; ++h) {
+            uint32_t v[kLdCols];
+            ptx::tmem_ld_32x32b_x32(taddr + c * kChunkCols + h * kLdCols, v);
+            ptx::tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < kLdCols / 2; ++i)
-            packed[c * (kLdCols / 2) + i] =
-                empty_split ? 0u
-                            : pack_half2(__uint_as_float(v[2 * i]) * alpha,
-                                         __uint_as_float(v[2 * i + 1]) * alpha);
+            for (int i = 0; i < kLdCols / 2; ++i)
+              packed[h * (kLdCols / 2) + i] =
+                  empty_split ? 0u
+                              : pack_half2(__uint_as_float(v[2 * i]) * alpha,
+                                           __uint_as_float(v[2 * i + 1]) * alpha);
+          }
+          if (c == kWarpCols / kChunkCols - 1) {
+            release_accumulator();
+            if (warp == kFirstEpilogueWarp && lane == 0) trace_stamp(p, 5, tile_iter, 1);
+          }
+          const int col = col0 + c * kChunkCols;
+          if (kChunkCols == 64 && staged) {
+            if (col < p.n) stage_and_store(packed, col);
+          } else {
+#pragma unroll
+            for (int i = 0; i < kChunkCols / 8; ++i) {
+              if (row_ok && col + 8 * i < p.n)
+                *reinterpret_cast<uint4*>(dst + c * kChunkCols + 8 * i) =
+                    make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+            }
+          }
         }
-        release_accumulator();
-        __half* dst = static_cast<__half*>(p.out) + t.split * p.out_split_stride + out_row * p.n + col0;
-#pragma unroll
-        for (int i = 0; i < kWarpCols / 8; ++i) {
-          if (row_ok && col0 + 8 * i < p.n)
-            *reinterpret_cast<uint4*>(dst + 8 * i) =
-                make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-        }
+        if (warp == kFirstEpilogueWarp && lane == 0) trace_stamp(p, 6, tile_iter, 0);
       }
       if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
     }
+    // shared memory must outlive the last box
+    if (lane == 0) ptx::bulk_wait_group<0>();
+    __syncwarp();
   }
 
   // ---- teardown

@@ -31,6 +31,11 @@ bool device_supported(const DeviceInfo& info);
 bool encode_tmap_2d_u8(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
                        uint32_t box_rows, uint32_t box_bytes, CUtensorMapSwizzle swizzle);
 
+// Tensor map for TMA stores of an FP16 / FP32 row-major matrix [rows, cols]: box of
+// [box_rows, box_cols] elements whose rows are 128 bytes, 128-byte swizzle.
+bool encode_tmap_2d_out(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                        bool is_f32, uint32_t box_rows, uint32_t box_cols);
+
 // Device word written by kernels whose bounded waits time out. One per loaded library.
 int* device_error_word();
 
