@@ -21,18 +21,19 @@
 //                      B, so a pair moves 1.5x fewer operand bytes per flop than two single
 //                      CTAs and fits a deeper pipeline. No multicast load is used anywhere.
 //
-// Structure of one CTA (512 threads, one CTA per SM):
+// Structure of one CTA (640 threads, one CTA per SM):
 //   warps 0, 2  loaders: TMA loads of the A tile / the B tile (128-byte swizzle) into a ring
 //               of shared-memory stages
 //   warp 3      scale loader: untiled bulk copies of the stage's scale atoms
-//   warps 4-7   scale movers, one per TMEM lane quarter: read the landed atoms from shared
-//               memory and write them into the stage's tensor-memory buffer with tcgen05.st
-//               (two wide stores per stage instead of a dozen tcgen05.cp, whose issue cost
-//               would exceed the MMA time of a stage), ahead of the MMAs
+//   warps 4-11  scale movers, two teams of one warp per TMEM lane quarter: read the landed atoms
+//               from shared memory and write them into the k-stage's tensor-memory buffer with
+//               tcgen05.st (two wide stores per stage instead of a dozen tcgen05.cp), ahead of
+//               the MMAs. One k-stage costs a mover ~700 cycles of waits, loads, stores and
+//               arrives against ~520 cycles of MMA work, so the teams take alternate k-stages.
 //   warp 1      MMA issuer (first CTA of a pair only): tcgen05.mma kind::mxf4nvf4
 //               (M x BN x 64 per instruction) accumulates FP32 in tensor memory;
 //               tcgen05.commit releases the stage / publishes the tile
-//   warps 8-15  epilogue: tcgen05.ld of the accumulator (a 32-lane quarter and half of the
+//   warps 12-19 epilogue: tcgen05.ld of the accumulator (a 32-lane quarter and half of the
 //               columns per warp), conversion, 16-byte stores with row / column predicates
 // All mbarrier waits are bounded (ptx::mbar_wait); a timeout is reported through
 // GemmParams::error instead of hanging.
@@ -57,8 +58,9 @@ constexpr int kWarpLoadA = 0;
 constexpr int kWarpMma = 1;
 constexpr int kWarpLoadB = 2;
 constexpr int kWarpLoadSf = 3;
-constexpr int kFirstSfMoverWarp = 4;    // four warps, one per TMEM lane quarter
-constexpr int kFirstEpilogueWarp = 8;
+constexpr int kFirstSfMoverWarp = 4;    // two teams of four warps (one warp per TMEM lane quarter)
+constexpr int kSfMoverTeams = 2;        // team t moves the scales of k-stages t, t + 2, t + 4, ...
+constexpr int kFirstEpilogueWarp = kFirstSfMoverWarp + 4 * kSfMoverTeams;
 constexpr int kGemmThreads = 32 * (kFirstEpilogueWarp + kEpilogueWarps);
 constexpr int kMaxStages = 8;
 constexpr int kMaxSfSlots = 16;
@@ -312,6 +314,12 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if constexpr (kTwoCta) ptx::cluster_sync();  // the partner's barriers are initialised too
   ptx::tc_fence_after_sync();
 
+  if ((p.debug & 64) && p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long ns;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+    p.trace[((0 * 8 + 7) * 64 + 63) * 2 + 0] = static_cast<unsigned long long>(clock64());
+    p.trace[((0 * 8 + 7) * 64 + 63) * 2 + 1] = ns;
+  }
   const uint32_t tmem_base = *tmem_holder;
   const int total_mt = s_cu_tiles[G];
   const int n_tiles = (p.n + BN - 1) / BN;
@@ -474,13 +482,14 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
     __syncwarp();
-  } else if (warp >= kFirstSfMoverWarp && warp < kFirstSfMoverWarp + 4) {
+  } else if (warp >= kFirstSfMoverWarp && warp < kFirstEpilogueWarp) {
     // ============================== scale movers =============================
     // Warp q moves a k-stage's scale atoms from the scale ring in shared memory into lanes
     // 32q..32q+31 of the stage's tensor-memory buffer (the MMA wants every 32-lane quarter to
     // hold the same 16 bytes per lane: row r of an atom lives in lane r % 32, column r / 32).
     // Lane t reads the 16 bytes at offset 16 t of each atom.
     const int q = warp & 3;
+    const int team = (warp - kFirstSfMoverWarp) >> 2;
     int stage = 0, slot = 0, iter = 0, sfbuf = 0;
     int lag_stage = 0, ahead = 0;   // operand stage of the k-stage sf_depth back; k-stages moved so far (saturates)
     uint32_t lag_phase = 0, slot_phase = 0;
@@ -490,6 +499,12 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int ks_begin = (k_stages * t.split) / p.num_splits;
       const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
       for (int ks = ks_begin; ks < ks_end; ++ks) {
+        // every warp walks all k-stages (ring positions and phases advance for both teams) but
+        // works only on its team's
+        const bool mine = (iter & (kSfMoverTeams - 1)) == team;
+        const bool need_lag = ahead >= sf_depth;
+        if (!need_lag) ++ahead;
+        if (mine) {
         // 1. atoms of this k-stage: shared memory -> registers
         // every lane polls (warp-uniform control flow: a single-lane wait costs a vote and a
         // broadcast per call, several hundred cycles per k-stage in this loop)
@@ -519,12 +534,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // 2. registers -> this k-stage's tensor-memory buffer, once the MMAs of the k-stage that
         //    used the buffer last (sf_depth k-stages ago) are done: their commit completes a
         //    phase of that k-stage's `empty` barrier
-        if (ahead < sf_depth) {
-          ++ahead;
-        } else {
-          if (!ptx::mbar_wait(empty_bar + lag_stage, lag_phase, abort_flag, 6)) { ok = false; break; }
-          if (++lag_stage == kStages) { lag_stage = 0; lag_phase ^= 1; }
-        }
+        if (need_lag && !ptx::mbar_wait(empty_bar + lag_stage, lag_phase, abort_flag, 6)) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t sf_taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                                   static_cast<uint32_t>(Cfg::kSfBase + sfbuf * Cfg::kSfColsPerBuf);
@@ -544,6 +554,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           ptx::mbar_arrive(sf_free_bar + slot);
         }
         if (q == 0 && lane == 0) trace_stamp(p, 3, iter, 1);
+        }
+        if (need_lag && ++lag_stage == kStages) { lag_stage = 0; lag_phase ^= 1; }
         if (++slot == kSfSlots) { slot = 0; slot_phase ^= 1; }
         ++iter;
         if (++sfbuf == sf_depth) sfbuf = 0;
@@ -586,10 +598,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool staged = kCanStage && p.tma_store != 0 && slab_full;
       // row coordinate of the slab in the output tensor map (split-K slices are stacked)
       const int map_row = s_row0[t.g] + t.mt * kTileM + slab_row + t.split * p.out_rows_per_split;
-      int ready = 1;
-      if (lane == 0) ready = ptx::mbar_wait(acc_full_bar + acc, acc_phase, abort_flag, 4) ? 1 : 0;
-      ready = __shfl_sync(0xffffffffu, ready, 0);
-      if (!ready) break;
+      if (!ptx::mbar_wait(acc_full_bar + acc, acc_phase, abort_flag, 4)) break;
       if (warp == kFirstEpilogueWarp && lane == 0) trace_stamp(p, 5, tile_iter, 0);
       ptx::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
@@ -602,11 +611,14 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           else ptx::mbar_arrive(acc_empty_bar + acc);
         }
       };
-      // 128 bytes (eight 16-byte units in w[0..31]) of this lane's row -> staging, then one TMA
-      // store of the slab's box at column `col`.
-      auto stage_and_store = [&](const uint32_t (&w)[32], int col) {
-        if (lane == 0) ptx::bulk_wait_group_read<0>();   // the previous box has left the buffer
+      // Staged output of 128 bytes per lane (eight 16-byte units in w[0..31]) in two steps, so
+      // that the accumulator can be released between them: fill the warp's staging buffer, then
+      // hand the 32 x 128-byte box at column `col` to the store engine.
+      auto wait_staging_free = [&]() {   // the previous box has left the buffer
+        if (lane == 0) ptx::bulk_wait_group_read<0>();
         __syncwarp();
+      };
+      auto fill_staging = [&](const uint32_t (&w)[32]) {
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
           const uint32_t addr = stg_row + (static_cast<uint32_t>(u ^ (lane & 7)) << 4);
@@ -615,6 +627,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        : "memory");
         }
         ptx::fence_proxy_async_smem();
+      };
+      auto store_staging = [&](int col) {
         __syncwarp();
         if (lane == 0) {
           ptx::tma_store_2d(&tmap_out, stg, col, map_row);
@@ -633,7 +647,11 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = empty_split ? 0u : __float_as_uint(__uint_as_float(v[i]) * alpha);
           if (staged) {
-            if (col0 + c * 32 < p.n) stage_and_store(v, col0 + c * 32);
+            if (col0 + c * 32 < p.n) {
+              wait_staging_free();
+              fill_staging(v);
+              store_staging(col0 + c * 32);
+            }
           } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -645,34 +663,78 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       } else {
         __half* dst = static_cast<__half*>(p.out) + out_row * p.n + col0;
         constexpr int kChunkCols = kWarpCols >= 64 ? 64 : kWarpCols;     // columns per pass
-#pragma unroll 1
-        for (int c = 0; c < kWarpCols / kChunkCols; ++c) {
-          uint32_t packed[32];
-#pragma unroll
-          for (int h = 0; h < kChunkCols / kLdCols; ++h) {
-            uint32_t v[kLdCols];
-            ptx::tmem_ld_32x32b_x32(taddr + c * kChunkCols + h * kLdCols, v);
-            ptx::tmem_ld_wait();
+        constexpr int kChunks = kWarpCols / kChunkCols;
+        // Chunk c is converted and put into the staging buffer while the box of chunk c - 1 is
+        // still on its way out only after that box has been read; the accumulator is released
+        // right after the last TMEM load, before the last box is handed over.
+        const bool plain = !empty_split && alpha == 1.0f;   // warp-uniform: no scaling needed
+        // 32 accumulator columns -> 16 packed half2 words
+        auto load_pack = [&](int col, uint32_t* packed) {
+          uint32_t v[kLdCols];
+          ptx::tmem_ld_32x32b_x32(taddr + col, v);
+          ptx::tmem_ld_wait();
+          if (plain) {
 #pragma unroll
             for (int i = 0; i < kLdCols / 2; ++i)
-              packed[h * (kLdCols / 2) + i] =
-                  empty_split ? 0u
-                              : pack_half2(__uint_as_float(v[2 * i]) * alpha,
-                                           __uint_as_float(v[2 * i + 1]) * alpha);
-          }
-          if (c == kWarpCols / kChunkCols - 1) {
-            release_accumulator();
-            if (warp == kFirstEpilogueWarp && lane == 0) trace_stamp(p, 5, tile_iter, 1);
-          }
-          const int col = col0 + c * kChunkCols;
-          if (kChunkCols == 64 && staged) {
-            if (col < p.n) stage_and_store(packed, col);
+              packed[i] = pack_half2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
           } else {
 #pragma unroll
-            for (int i = 0; i < kChunkCols / 8; ++i) {
-              if (row_ok && col + 8 * i < p.n)
-                *reinterpret_cast<uint4*>(dst + c * kChunkCols + 8 * i) =
-                    make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+            for (int i = 0; i < kLdCols / 2; ++i)
+              packed[i] = empty_split ? 0u
+                                      : pack_half2(__uint_as_float(v[2 * i]) * alpha,
+                                                   __uint_as_float(v[2 * i + 1]) * alpha);
+          }
+        };
+        auto direct_store = [&](int c, const uint32_t (&packed)[32]) {
+#pragma unroll
+          for (int i = 0; i < kChunkCols / 8; ++i) {
+            if (row_ok && col0 + c * kChunkCols + 8 * i < p.n)
+              *reinterpret_cast<uint4*>(dst + c * kChunkCols + 8 * i) =
+                  make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+          }
+        };
+        const bool use_staging = kChunkCols == 64 && staged;
+        if constexpr (kChunks == 2 && kChunkCols == 64) {
+          // 128 columns per warp: the whole slab is converted into registers first, so the
+          // accumulator goes back to the MMA warp before any output leaves the registers
+          uint32_t p0[32], p1[32];
+          load_pack(0, p0);
+          load_pack(32, p0 + 16);
+          load_pack(64, p1);
+          load_pack(96, p1 + 16);
+          release_accumulator();
+          if (warp == kFirstEpilogueWarp && lane == 0) trace_stamp(p, 5, tile_iter, 1);
+          if (use_staging) {
+            wait_staging_free();
+            if (col0 < p.n) { fill_staging(p0); store_staging(col0); }
+            if (col0 + 64 < p.n) {
+              wait_staging_free();
+              fill_staging(p1);
+              store_staging(col0 + 64);
+            }
+          } else {
+            direct_store(0, p0);
+            direct_store(1, p1);
+          }
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < kChunks; ++c) {
+            uint32_t packed[32];
+#pragma unroll
+            for (int h = 0; h < kChunkCols / kLdCols; ++h) load_pack(c * kChunkCols + h * kLdCols, packed + 16 * h);
+            if (c == kChunks - 1) {
+              release_accumulator();
+              if (warp == kFirstEpilogueWarp && lane == 0) trace_stamp(p, 5, tile_iter, 1);
+            }
+            const int col = col0 + c * kChunkCols;
+            if (use_staging) {
+              if (col < p.n) {
+                wait_staging_free();
+                fill_staging(packed);
+                store_staging(col);
+              }
+            } else {
+              direct_store(c, packed);
             }
           }
         }
@@ -687,6 +749,12 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   // ---- teardown
   __syncthreads();
+  if ((p.debug & 64) && p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long ns;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+    p.trace[((0 * 8 + 7) * 64 + 62) * 2 + 0] = static_cast<unsigned long long>(clock64());
+    p.trace[((0 * 8 + 7) * 64 + 62) * 2 + 1] = ns;
+  }
   // In a pair neither CTA may leave (or free tensor memory) while the other can still
   // signal its barriers or read its shared memory.
   if constexpr (kTwoCta) ptx::cluster_sync();
