@@ -1,0 +1,135 @@
+"""Full-size cases of the two multi-GPU configurations, run on one GPU:
+
+  * the N-sharded GEMM (M=16384, N=28672, K=8192): every rank's column block, computed as that
+    rank would compute it, against the oracle on sampled rows x columns and against the same
+    columns of a wider launch (a shard is a plain GEMM over a slice of B and its scale tiles);
+  * the DeepSeek-V3-shaped routed MoE layer (T=4096, H=7168, I=2048, 256 experts, top-8):
+    sampled tokens against the oracle with the layer's full weights, plus properties that do
+    not depend on size (routing is a permutation, doubling the route weights doubles the output).
+
+Operands are synthetic: random E2M1 payload bytes and UE4M3 scale codes drawn on the GPU, so
+that no multi-gigabyte tensor is quantised on the CPU.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import check_gemm_parity, topk_routing
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import sm120_nvfp4_b200 as pkg
+    from sm120_nvfp4_b200 import _lib
+    _lib.lib()
+    _lib.lib().b200_nvfp4_set_tile_n(0)
+    yield pkg
+    assert _lib.device_error() == 0
+
+
+def _payload(shape, gen):
+    return torch.randint(0, 256, shape, dtype=torch.uint8, device="cuda", generator=gen)
+
+
+def _scales(count, lo, hi, gen):
+    return torch.randint(lo, hi, (count,), dtype=torch.uint8, device="cuda", generator=gen)
+
+
+def test_config5_n_sharded_column_blocks(ops):
+    m, n, k, world = 16384, 28672, 8192, 8
+    n_rank = n // world
+    assert n_rank % 128 == 0                      # scale tiles of B split cleanly between ranks
+    g = torch.Generator(device="cuda").manual_seed(0xB2000500)
+    a = _payload((m, k // 2), g)
+    b = _payload((n, k // 2), g)
+    sfa = _scales(ops.scale_a_elements(m, n, k), 0x2c, 0x38, g)
+    sfb = _scales(ops.scale_b_elements(m, n, k), 0x2c, 0x38, g)
+    skp = ops.scale_k_padded(k)
+    rng = np.random.default_rng(5)
+    rows = np.sort(rng.choice(m, size=12, replace=False)).astype(np.int32)
+    a_rows = a[torch.from_numpy(rows).cuda().long()].cpu().numpy()
+    # scale rows of the sampled A rows, re-laid into a region of their own for the oracle
+    nkb = k // 16
+    r_idx = np.repeat(rows, nkb)
+    kb_idx = np.tile(np.arange(nkb, dtype=np.int32), rows.size)
+    sfa_host = sfa.cpu().numpy()
+    sfa_small = np.zeros(oracle.scale_region_bytes(rows.size, k), np.uint8)
+    sfa_small[oracle.sf_offsets(np.repeat(np.arange(rows.size, dtype=np.int32), nkb), kb_idx, k)] = \
+        sfa_host[oracle.sf_offsets(r_idx, kb_idx, k)]
+    wide = None
+    for rank in (0, 3, 7):
+        b_r = b[rank * n_rank:(rank + 1) * n_rank]
+        sfb_r = sfb[rank * n_rank * skp:(rank + 1) * n_rank * skp]
+        out = ops.gemm(a, b_r, sfa, sfb_r)                       # what rank `rank` runs
+        assert tuple(out.shape) == (m, n_rank)
+        cols = np.sort(rng.choice(n_rank, size=96, replace=False)).astype(np.int32)
+        ref = oracle.gemm_sampled(a_rows, b_r.cpu().numpy(), sfa_small, sfb_r.cpu().numpy(),
+                                  np.arange(rows.size, dtype=np.int32), cols)
+        got = out[torch.from_numpy(rows).cuda().long()].cpu().numpy()[:, cols]
+        check_gemm_parity(got, ref)
+        if rank == 3:   # the same columns out of a launch over ranks 2..3 together: bit-identical
+            b_w = b[2 * n_rank:4 * n_rank]
+            sfb_w = sfb[2 * n_rank * skp:4 * n_rank * skp]
+            wide = ops.gemm(a, b_w, sfa, sfb_w)
+            assert torch.equal(wide[:, n_rank:], out)
+        del out
+    del wide
+
+
+def test_config4_full_size_moe_sampled_tokens_and_properties(ops):
+    t, hidden, inter, experts, topk = 4096, 7168, 2048, 256, 8
+    g = torch.Generator(device="cuda").manual_seed(0xB2000400)
+    gw = _payload((experts, 2 * inter, hidden // 2), g)
+    dw = _payload((experts, hidden, inter // 2), g)
+    gws = _scales(experts * 2 * inter * ops.scale_k_padded(hidden), 0x04, 0x0c, g).view(experts, -1)
+    dws = _scales(experts * hidden * ops.scale_k_padded(inter), 0x04, 0x0c, g).view(experts, -1)
+    x = torch.randn((t, hidden), device="cuda", generator=g).to(torch.bfloat16)
+    ids_np, w_np = topk_routing(t, experts, topk, 4)
+    ids, w = torch.from_numpy(ids_np).cuda(), torch.from_numpy(w_np).cuda()
+    seq = torch.tensor([t], dtype=torch.int32, device="cuda")
+    cu = torch.tensor([0, t], dtype=torch.int32, device="cuda")
+    xq, xs = ops.quantize_expert(x, seq, cu, scale_m_pad=t)
+    out = ops.fused_moe(xq, xs.flatten(), gw, gws, dw, dws, ids, w)
+    torch.cuda.synchronize()
+    assert tuple(out.shape) == (t, hidden) and bool(torch.isfinite(out).all())
+
+    # routing of the whole layer: a permutation of [0, T*k) grouped by expert
+    from sm120_nvfp4_b200 import _lib
+    L = _lib.lib()
+    pos = torch.empty((t, topk), dtype=torch.int32, device="cuda")
+    seqlens = torch.empty(experts, dtype=torch.int32, device="cuda")
+    cus = torch.empty(experts + 1, dtype=torch.int32, device="cuda")
+    assert L.b200_nvfp4_moe_route(ids.data_ptr(), pos.data_ptr(), seqlens.data_ptr(), cus.data_ptr(), t, topk,
+                                  experts, 0, torch.cuda.current_stream().cuda_stream) == 0
+    flat = ids_np.reshape(-1)
+    order = np.argsort(flat, kind="stable")
+    want_pos = np.empty_like(flat)
+    want_pos[order] = np.arange(flat.size, dtype=np.int32)
+    np.testing.assert_array_equal(pos.cpu().numpy().reshape(-1), want_pos)
+    np.testing.assert_array_equal(seqlens.cpu().numpy(), np.bincount(flat, minlength=experts))
+    assert int(cus[-1]) == t * topk
+
+    # doubling every route weight doubles the layer output exactly (power of two, FP32 combine)
+    out2 = ops.fused_moe(xq, xs.flatten(), gw, gws, dw, dws, ids, w * 2)
+    sel = torch.isfinite(out2) & (out.abs() >= 2.0 ** -13)
+    assert torch.equal(out2[sel], (out * 2)[sel])
+
+    # sampled tokens against the oracle, which runs the same layer on those tokens alone (a
+    # token's output depends on no other token)
+    rng = np.random.default_rng(44)
+    sample = np.sort(rng.choice(t, size=6, replace=False))
+    sel_t = torch.from_numpy(sample).cuda().long()
+    xb = x[sel_t].view(torch.int16).cpu().numpy().view(np.uint16)
+    sx, sxs = oracle.quantize_expert(xb, [sample.size], [0, sample.size], 128, True)
+    np.testing.assert_array_equal(xq[sel_t].cpu().numpy(), sx)      # the quantiser, bit for bit
+    want, *_ = oracle.fused_moe(sx, sxs.ravel(), gw.cpu().numpy(), gws.cpu().numpy(), dw.cpu().numpy(),
+                                dws.cpu().numpy(), ids_np[sample], w_np[sample])
+    got = out[sel_t].cpu().numpy()
+    num = np.linalg.norm(got.astype(np.float64) - want.astype(np.float64))
+    den = np.linalg.norm(want.astype(np.float64))
+    assert num / den < 2e-2, num / den                              # same gate as the small-layer test
