@@ -267,6 +267,10 @@ def run_gemm(args, world, rank, device, peaks):
 
     fp4_peak = 4.0 * peaks["bf16_tflops"]
     achieved = wl.flops_rank / (float(np.mean(per_step)) * 1e-3) / 1e12
+    # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from one ncu capture of this
+    # kernel on this workload (profiles/: the DRAM-traffic summary of the 8192^3 case and the
+    # full capture of the 4096 x 4096 x 8192 case); not captured for the sharded workload
+    ncu_traffic = {"gemm8192": 266.65e6, "gemm4096": 42.6e6}.get(args.workload) if world == 1 else None
     line = {
         "metric": "NVFP4 GEMM TFLOPS (% FP4 peak); fused-MoE tokens/s at 1/2/4/8 B200",
         "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -279,7 +283,8 @@ def run_gemm(args, world, rank, device, peaks):
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s",
-                     "frac": achieved / fp4_peak, "traffic": None,
+                     "frac": achieved / fp4_peak, "traffic": ncu_traffic,
+                     "algorithmic_bytes": wl.bytes_rank if hasattr(wl, "bytes_rank") else None,
                      "peak_source": f"4 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']:.0f} TF/s): "
                                     "no FP4 figure is measured on this pool; FP4 : BF16 nominal ratio is 4",
                      "frac_of_nominal_9pf": achieved / NOMINAL_FP4_TFLOPS,
