@@ -235,7 +235,11 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   int* s_row0 = s_cu_tiles + (p.num_groups + 1);
   int* s_rows = s_row0 + (p.num_groups + 1);
 
-  const int warp = threadIdx.x >> 5;
+  // The warp index comes out of a shuffle so that the compiler can prove it uniform across the
+  // warp: the role branches below then are uniform branches, and the barrier addresses, ring
+  // positions and descriptors inside them stay in uniform registers instead of being moved
+  // there from vector registers for every mbarrier / TMA / tcgen05 instruction.
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
   const int G = p.num_groups;
   const uint32_t cta_rank = kTwoCta ? ptx::cluster_cta_rank() : 0u;
@@ -328,6 +332,18 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int k_stages = (kt + 3) / 4;            // pipeline stages along K
   const int n_sf_tiles = (p.n + 127) / 128;     // 128-row scale tiles of B
 
+  // 32-bit shared-window addresses of the rings: the role loops below advance them with adds.
+  const uint32_t stage_u32 = ptx::smem_u32(stage_base);
+  const uint32_t sf_u32 = ptx::smem_u32(sf_base);
+  const uint32_t full_u32 = ptx::smem_u32(full_bar);
+  const uint32_t empty_u32 = ptx::smem_u32(empty_bar);
+  const uint32_t sf_landed_u32 = ptx::smem_u32(sf_landed_bar);
+  const uint32_t sf_free_u32 = ptx::smem_u32(sf_free_bar);
+  // where arrivals for a stage's `full` barrier go: this CTA's barrier, or the leader's
+  const uint32_t full_target_u32 = kTwoCta ? ptx::map_to_cta(full_u32, 0) : full_u32;
+  const bool tracing = (p.debug & 64) != 0 && p.trace != nullptr && blockIdx.x < 2;
+  const int k_stages_full = kt / 4;             // k-stages with all four atoms
+
   if (warp == kWarpLoadA || warp == kWarpLoadB) {
     // ============================ operand loaders ============================
     // One thread per operand. Completion bytes are counted on the barrier of the first CTA
@@ -337,35 +353,38 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool is_a = warp == kWarpLoadA;
       const CUtensorMap* tmap = is_a ? &tmap_a : &tmap_b;
       const uint32_t bytes = is_a ? Cfg::kABytes : Cfg::kBBytes;
+      const uint32_t dst0 = stage_u32 + (is_a ? 0 : Cfg::kABytes);
+      const bool no_loads = (p.debug & 2) != 0;   // experiment: barriers only
       int stage = 0, iter = 0;
-      uint32_t phase = 0;
-      bool ok = true, peeked = false;
+      uint32_t phase = 0, dst = dst0, full_a = full_u32, full_t = full_target_u32, empty_a = empty_u32;
+      bool ok = true;
       for (int task = worker; task < total_tasks && ok; task += num_workers) {
         TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
         const int row = is_a ? s_row0[t.g] + t.mt * kTileM + static_cast<int>(cta_rank) * kBlockM
                              : t.g * p.b_group_rows + t.nt * BN + static_cast<int>(cta_rank) * Cfg::kBRows;
         const int ks_begin = (k_stages * t.split) / p.num_splits;
         const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
-        for (int ks = ks_begin; ks < ks_end; ++ks) {
-          if (lane == 0) trace_stamp(p, is_a ? 0 : 4, iter, 0);
-          if (!peeked && !ptx::mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, 1)) { ok = false; break; }
-          if (lane == 0) trace_stamp(p, is_a ? 0 : 4, iter, 1);
+        int c0 = ks_begin * kStageKBytes;
+        for (int ks = ks_begin; ks < ks_end; ++ks, c0 += kStageKBytes) {
+          if (tracing && lane == 0) trace_stamp(p, is_a ? 0 : 4, iter, 0);
+          if (!ptx::mbar_wait(empty_a, phase ^ 1, abort_flag, 1)) { ok = false; break; }
+          if (tracing && lane == 0) trace_stamp(p, is_a ? 0 : 4, iter, 1);
           ++iter;
-          uint8_t* dst = stage_base + stage * Cfg::kStageBytes + (is_a ? 0 : Cfg::kABytes);
-          if (p.debug & 2) {   // experiment: no operand traffic, barriers only
-            if (ptx::elect_one() && leader) ptx::mbar_arrive(full_bar + stage);
-          } else if (ptx::elect_one()) {
-            if constexpr (kTwoCta) {
-              if (leader) ptx::mbar_arrive_expect_tx(full_bar + stage, 2 * bytes);
-              ptx::tma_load_2d_pair(dst, tmap, ptx::map_to_cta(full_bar + stage, 0), ks * kStageKBytes, row);
+          if (ptx::elect_one()) {
+            if (no_loads) {
+              if (leader) ptx::mbar_arrive(full_a);
+            } else if constexpr (kTwoCta) {
+              if (leader) ptx::mbar_arrive_expect_tx(full_a, 2 * bytes);
+              ptx::tma_load_2d_pair(dst, tmap, full_t, c0, row);
             } else {
-              ptx::mbar_arrive_expect_tx(full_bar + stage, bytes);
-              ptx::tma_load_2d(dst, tmap, full_bar + stage, ks * kStageKBytes, row);
+              ptx::mbar_arrive_expect_tx(full_a, bytes);
+              ptx::tma_load_2d(dst, tmap, full_a, c0, row);
             }
           }
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
-          // probe the next stage now; the answer is used at the top of the next iteration
-          peeked = __all_sync(0xffffffffu, ptx::mbar_test_wait(empty_bar + stage, phase ^ 1));
+          dst += Cfg::kStageBytes; full_a += 8; full_t += 8; empty_a += 8;
+          if (++stage == kStages) {
+            stage = 0; phase ^= 1; dst = dst0; full_a = full_u32; full_t = full_target_u32; empty_a = empty_u32;
+          }
         }
       }
     }
@@ -375,42 +394,41 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // Fills the scale-atom ring: waits for a slot the movers have drained, then bulk-copies
     // the k-stage's SFA atoms and SFB atoms into it.
     {
-      int stage = 0, iter = 0;
-      uint32_t phase = 0;
+      const bool no_loads = (p.debug & 8) != 0;   // experiment: no scale traffic
+      int slot = 0, iter = 0;
+      uint32_t phase = 0, dst = sf_u32, landed_a = sf_landed_u32, free_a = sf_free_u32;
       bool ok = true;
       for (int task = worker; task < total_tasks && ok; task += num_workers) {
         TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
-        const uint8_t* sfa_tile =
-            p.sfa + t.g * p.sfa_group_stride +
-            static_cast<long long>(t.mt * kCtas + static_cast<int>(cta_rank)) * kt * kAtomBytes;
         const int sf_tile0 = (t.nt * BN) / 128;
-        const uint8_t* sfb_tile = p.sfb + t.g * p.sfb_group_stride +
-                                  static_cast<long long>(sf_tile0) * kt * kAtomBytes;
         int sfb_groups = Cfg::kSfbGroups;
         if (sf_tile0 + sfb_groups > n_sf_tiles) sfb_groups = n_sf_tiles - sf_tile0;
         const int ks_begin = (k_stages * t.split) / p.num_splits;
         const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
-        for (int ks = ks_begin; ks < ks_end; ++ks) {
-          if (!ptx::mbar_wait(sf_free_bar + stage, phase ^ 1, abort_flag, 8)) { ok = false; break; }
-          if (lane == 0) trace_stamp(p, 2, iter, 0);
-          uint8_t* ssfa = sf_base + stage * Cfg::kSfSlotBytes;
-          uint8_t* ssfb = ssfa + Cfg::kSfaBytes;
-          const int atoms = min(4, kt - ks * 4);
-          const uint32_t sf_bytes = static_cast<uint32_t>(atoms) * kAtomBytes;
-          if (p.debug & 8) {   // experiment: no scale traffic
-            if (ptx::elect_one()) ptx::mbar_arrive(sf_landed_bar + stage);
-          } else if (ptx::elect_one()) {
-            ptx::mbar_arrive_expect_tx(sf_landed_bar + stage, sf_bytes * (1 + sfb_groups));
-            ptx::bulk_load(ssfa, sfa_tile + static_cast<long long>(ks) * 4 * kAtomBytes, sf_bytes,
-                           sf_landed_bar + stage);
-            for (int gi = 0; gi < sfb_groups; ++gi)
-              ptx::bulk_load(ssfb + gi * 4 * kAtomBytes,
-                             sfb_tile + (static_cast<long long>(gi) * kt + ks * 4) * kAtomBytes,
-                             sf_bytes, sf_landed_bar + stage);
+        const uint8_t* sfa_src = p.sfa + t.g * p.sfa_group_stride +
+                                 (static_cast<long long>(t.mt * kCtas + static_cast<int>(cta_rank)) * kt + ks_begin * 4) * kAtomBytes;
+        const uint8_t* sfb_src = p.sfb + t.g * p.sfb_group_stride +
+                                 (static_cast<long long>(sf_tile0) * kt + ks_begin * 4) * kAtomBytes;
+        const long long sfb_group_step = static_cast<long long>(kt) * kAtomBytes;
+        for (int ks = ks_begin; ks < ks_end; ++ks, sfa_src += 4 * kAtomBytes, sfb_src += 4 * kAtomBytes) {
+          if (!ptx::mbar_wait(free_a, phase ^ 1, abort_flag, 8)) { ok = false; break; }
+          if (tracing && lane == 0) trace_stamp(p, 2, iter, 0);
+          const uint32_t sf_bytes = ks < k_stages_full ? 4u * kAtomBytes : static_cast<uint32_t>(kt - ks * 4) * kAtomBytes;
+          if (ptx::elect_one()) {
+            if (no_loads) {
+              ptx::mbar_arrive(landed_a);
+            } else {
+              ptx::mbar_arrive_expect_tx(landed_a, sf_bytes * (1 + sfb_groups));
+              ptx::bulk_load(dst, sfa_src, sf_bytes, landed_a);
+              ptx::bulk_load(dst + Cfg::kSfaBytes, sfb_src, sf_bytes, landed_a);
+              if (Cfg::kSfbGroups == 2 && sfb_groups == 2)
+                ptx::bulk_load(dst + Cfg::kSfaBytes + 4 * kAtomBytes, sfb_src + sfb_group_step, sf_bytes, landed_a);
+            }
           }
-          if (lane == 0) trace_stamp(p, 2, iter, 1);
+          if (tracing && lane == 0) trace_stamp(p, 2, iter, 1);
           ++iter;
-          if (++stage == kSfSlots) { stage = 0; phase ^= 1; }
+          dst += Cfg::kSfSlotBytes; landed_a += 8; free_a += 8;
+          if (++slot == kSfSlots) { slot = 0; phase ^= 1; dst = sf_u32; landed_a = sf_landed_u32; free_a = sf_free_u32; }
         }
       }
     }
@@ -420,9 +438,13 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (leader) {
       constexpr uint32_t idesc = ptx::make_idesc_nvfp4(kTileM, BN);
       constexpr uint16_t kAllCtas = kTwoCta ? 3 : 1;
+      constexpr uint32_t kDescStep = Cfg::kStageBytes >> 4;        // descriptor units per stage
+      const uint32_t a_lo0 = ptx::kmajor_sw128_desc_lo(stage_u32);
+      const uint32_t sf_col0 = tmem_base + Cfg::kSfBase;
+      const bool no_mma = (p.debug & 1) != 0;   // experiment: data path only
       int stage = 0, acc = 0, iter = 0, sfbuf = 0;
-      uint32_t phase = 0, acc_phase = 0;
-      bool ok = true, peeked = false;
+      uint32_t phase = 0, acc_phase = 0, full_a = full_u32, empty_a = empty_u32, a_lo = a_lo0, sf_col = sf_col0;
+      bool ok = true;
       for (int task = worker; task < total_tasks && ok; task += num_workers) {
         TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
         const int ks_begin = (k_stages * t.split) / p.num_splits;
@@ -430,51 +452,60 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // A tile narrower than 128 columns uses part of a 128-row scale atom: column
         // (n0 % 128) / 32 of the four TMEM columns the atom occupies.
         const uint32_t sfb_sub = BN < 128 ? static_cast<uint32_t>(((t.nt * BN) % 128) / 32) : 0u;
-        if (lane == 0) trace_stamp(p, 7, iter / 32, 0);
+        if (tracing && lane == 0) trace_stamp(p, 7, iter / 32, 0);
         if (!ptx::mbar_wait(acc_empty_bar + acc, acc_phase ^ 1, abort_flag, 2)) break;
-        if (lane == 0) trace_stamp(p, 7, iter / 32, 1);
+        if (tracing && lane == 0) trace_stamp(p, 7, iter / 32, 1);
         ptx::tc_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * BN);
+        // The tensor pipe accepts an MMA only when the previous one is almost done (issuing
+        // four 128-cycle MMAs occupies this thread for 512 cycles), so whatever this thread does
+        // between the last MMA of a k-stage and the first of the next must fit into one MMA's
+        // run time or the pipe idles. The next stage's barrier is therefore probed between the
+        // third and the fourth MMA, while the pipe is busy.
+        bool ready = false;
         for (int ks = ks_begin; ks < ks_end; ++ks) {
-          // The stage was probed while the previous stage's MMAs were being issued; only
-          // fall back to a real wait when that probe came too early.
-          if (lane == 0) trace_stamp(p, 1, iter, 0);
-          if (!peeked && !ptx::mbar_wait(full_bar + stage, phase, abort_flag, 3)) { ok = false; break; }
-          if (lane == 0) trace_stamp(p, 1, iter, 1);
+          if (tracing && lane == 0) trace_stamp(p, 1, iter, 0);
+          if (!ready && !ptx::mbar_wait(full_a, phase, abort_flag, 3)) { ok = false; break; }
+          if (tracing && lane == 0) trace_stamp(p, 1, iter, 1);
           ptx::tc_fence_after_sync();
-          const int next_stage = stage + 1 == kStages ? 0 : stage + 1;
-          peeked = __all_sync(0xffffffffu, ptx::mbar_test_wait(full_bar + next_stage, next_stage == 0 ? phase ^ 1 : phase));
-          const uint32_t a_addr = ptx::smem_u32(stage_base + stage * Cfg::kStageBytes);
-          const uint32_t b_addr = a_addr + Cfg::kABytes;
-          const int atoms = min(4, kt - ks * 4);
-          const uint32_t sfa_col = tmem_base + Cfg::kSfBase + sfbuf * Cfg::kSfColsPerBuf;
-          const uint32_t sfb_col = sfa_col + 16 + sfb_sub;
-          const uint64_t a_desc = ptx::make_kmajor_sw128_desc(a_addr);
-          const uint64_t b_desc = ptx::make_kmajor_sw128_desc(b_addr);
-          const uint32_t accumulate_first = ks > ks_begin ? 1u : 0u;
-          if (ptx::elect_one()) {
-            // 64 E2M1 values = 32 bytes along K: +2 in the descriptor's 16-byte address field
-            if (p.debug & 1) {   // experiment: data path only, no MMAs
-            } else if (atoms == 4) {
-              ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_desc, b_desc, idesc, sfa_col, sfb_col, accumulate_first);
-              ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_desc + 2, b_desc + 2, idesc, sfa_col + 4,
+          const uint32_t b_lo = a_lo + (Cfg::kABytes >> 4);
+          const uint32_t sfb_col = sf_col + 16 + sfb_sub;
+          const bool full_stage = ks < k_stages_full;
+          const bool last_ring = stage + 1 == kStages;
+          const uint32_t next_full = last_ring ? full_u32 : full_a + 8;
+          const uint32_t next_phase = last_ring ? phase ^ 1 : phase;
+          // 64 E2M1 values = 32 bytes along K: +2 in the descriptor's 16-byte address field
+          if (full_stage && !no_mma) {
+            if (ptx::elect_one()) {
+              ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_lo, b_lo, ptx::kKmajorSw128DescHi, idesc, sf_col, sfb_col,
+                                       ks > ks_begin ? 1u : 0u);
+              ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_lo + 2, b_lo + 2, ptx::kKmajorSw128DescHi, idesc, sf_col + 4,
                                        sfb_col + Cfg::kSfbColsPerMma, 1u);
-              ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_desc + 4, b_desc + 4, idesc, sfa_col + 8,
+              ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_lo + 4, b_lo + 4, ptx::kKmajorSw128DescHi, idesc, sf_col + 8,
                                        sfb_col + 2 * Cfg::kSfbColsPerMma, 1u);
-              ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_desc + 6, b_desc + 6, idesc, sfa_col + 12,
-                                       sfb_col + 3 * Cfg::kSfbColsPerMma, 1u);
-            } else {
-              for (int j = 0; j < atoms; ++j)
-                ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_desc + 2 * j, b_desc + 2 * j, idesc,
-                                         sfa_col + 4 * j, sfb_col + j * Cfg::kSfbColsPerMma,
-                                         j > 0 ? 1u : accumulate_first);
             }
-            ptx::tc_commit<kCtas>(empty_bar + stage, kAllCtas);
+            ready = ks + 1 < ks_end && __all_sync(0xffffffffu, ptx::mbar_test_wait(next_full, next_phase));
+            if (ptx::elect_one()) {
+              ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_lo + 6, b_lo + 6, ptx::kKmajorSw128DescHi, idesc, sf_col + 12,
+                                       sfb_col + 3 * Cfg::kSfbColsPerMma, 1u);
+              ptx::tc_commit<kCtas>(empty_a, kAllCtas);
+            }
+          } else {
+            ready = false;
+            if (ptx::elect_one()) {
+              const int atoms = no_mma ? 0 : kt - ks * 4;
+              for (int j = 0; j < atoms && j < 4; ++j)
+                ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_lo + 2 * j, b_lo + 2 * j, ptx::kKmajorSw128DescHi, idesc,
+                                         sf_col + 4 * j, sfb_col + j * Cfg::kSfbColsPerMma,
+                                         (j > 0 || ks > ks_begin) ? 1u : 0u);
+              ptx::tc_commit<kCtas>(empty_a, kAllCtas);
+            }
           }
           ++iter;
-          if (++sfbuf == sf_depth) sfbuf = 0;
-          stage = next_stage;
-          if (stage == 0) phase ^= 1;
+          sf_col += Cfg::kSfColsPerBuf;
+          if (++sfbuf == sf_depth) { sfbuf = 0; sf_col = sf_col0; }
+          full_a += 8; empty_a += 8; a_lo += kDescStep;
+          if (++stage == kStages) { stage = 0; phase ^= 1; full_a = full_u32; empty_a = empty_u32; a_lo = a_lo0; }
         }
         if (!ok) break;
         if (ptx::elect_one()) ptx::tc_commit<kCtas>(acc_full_bar + acc, kAllCtas);
@@ -484,15 +515,20 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     __syncwarp();
   } else if (warp >= kFirstSfMoverWarp && warp < kFirstEpilogueWarp) {
     // ============================== scale movers =============================
-    // Warp q moves a k-stage's scale atoms from the scale ring in shared memory into lanes
-    // 32q..32q+31 of the stage's tensor-memory buffer (the MMA wants every 32-lane quarter to
-    // hold the same 16 bytes per lane: row r of an atom lives in lane r % 32, column r / 32).
-    // Lane t reads the 16 bytes at offset 16 t of each atom.
+    // Warp q of a team moves a k-stage's scale atoms from the scale ring in shared memory into
+    // lanes 32q..32q+31 of the k-stage's tensor-memory buffer (the MMA wants every 32-lane
+    // quarter to hold the same 16 bytes per lane: row r of an atom lives in lane r % 32,
+    // column r / 32). Lane t reads the 16 bytes at offset 16 t of each atom.
     const int q = warp & 3;
     const int team = (warp - kFirstSfMoverWarp) >> 2;
+    const bool no_store = (p.debug & 4) != 0;   // experiment: skip the tensor-memory stores
+    const uint32_t lane_off = static_cast<uint32_t>(lane) * 16;
+    const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(Cfg::kSfBase);
     int stage = 0, slot = 0, iter = 0, sfbuf = 0;
-    int lag_stage = 0, ahead = 0;   // operand stage of the k-stage sf_depth back; k-stages moved so far (saturates)
+    int lag_stage = 0, ahead = 0;   // operand stage of the k-stage sf_depth back; k-stages walked so far (saturates)
     uint32_t lag_phase = 0, slot_phase = 0;
+    uint32_t src = sf_u32 + lane_off, landed_a = sf_landed_u32, free_a = sf_free_u32, full_t = full_target_u32;
+    uint32_t lag_a = empty_u32, taddr = taddr0;
     bool ok = true;
     for (int task = worker; task < total_tasks && ok; task += num_workers) {
       TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
@@ -505,61 +541,62 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const bool need_lag = ahead >= sf_depth;
         if (!need_lag) ++ahead;
         if (mine) {
-        // 1. atoms of this k-stage: shared memory -> registers
-        // every lane polls (warp-uniform control flow: a single-lane wait costs a vote and a
-        // broadcast per call, several hundred cycles per k-stage in this loop)
-        if (!ptx::mbar_wait(sf_landed_bar + slot, slot_phase, abort_flag, 5)) { ok = false; break; }
-        if (q == 0 && lane == 0) trace_stamp(p, 3, iter, 0);
-        const uint8_t* ssfa = sf_base + slot * Cfg::kSfSlotBytes + lane * 16;
-        const uint8_t* ssfb = ssfa + Cfg::kSfaBytes;
-        const int atoms = min(4, kt - ks * 4);
-        uint32_t ra[16];
+          // 1. atoms of this k-stage: shared memory -> registers. Every lane polls: a
+          //    single-lane wait costs a vote and a broadcast per call.
+          if (!ptx::mbar_wait(landed_a, slot_phase, abort_flag, 5)) { ok = false; break; }
+          if (tracing && q == 0 && lane == 0) trace_stamp(p, 3, iter, 0);
+          const int atoms = ks < k_stages_full ? 4 : kt - ks * 4;
+          uint32_t ra[16];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 v = make_uint4(0u, 0u, 0u, 0u);
-          if (j < atoms) v = *reinterpret_cast<const uint4*>(ssfa + j * kAtomBytes);
-          ra[4 * j] = v.x; ra[4 * j + 1] = v.y; ra[4 * j + 2] = v.z; ra[4 * j + 3] = v.w;
-        }
-        uint32_t rb[4 * Cfg::kSfbColsPerMma];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-#pragma unroll
-          for (int gi = 0; gi < Cfg::kSfbGroups; ++gi) {
+          for (int j = 0; j < 4; ++j) {
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (j < atoms) v = *reinterpret_cast<const uint4*>(ssfb + (gi * 4 + j) * kAtomBytes);
-            const int c = j * Cfg::kSfbColsPerMma + 4 * gi;
-            rb[c] = v.x; rb[c + 1] = v.y; rb[c + 2] = v.z; rb[c + 3] = v.w;
+            if (j < atoms) v = ptx::ld_shared_v4(src + j * kAtomBytes);
+            ra[4 * j] = v.x; ra[4 * j + 1] = v.y; ra[4 * j + 2] = v.z; ra[4 * j + 3] = v.w;
           }
+          uint32_t rb[4 * Cfg::kSfbColsPerMma];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int gi = 0; gi < Cfg::kSfbGroups; ++gi) {
+              uint4 v = make_uint4(0u, 0u, 0u, 0u);
+              if (j < atoms) v = ptx::ld_shared_v4(src + Cfg::kSfaBytes + (gi * 4 + j) * kAtomBytes);
+              const int c = j * Cfg::kSfbColsPerMma + 4 * gi;
+              rb[c] = v.x; rb[c + 1] = v.y; rb[c + 2] = v.z; rb[c + 3] = v.w;
+            }
+          }
+          // 2. registers -> this k-stage's tensor-memory buffer, once the MMAs of the k-stage
+          //    that used the buffer last (sf_depth k-stages ago) are done: their commit
+          //    completes a phase of that k-stage's `empty` barrier
+          if (need_lag && !ptx::mbar_wait(lag_a, lag_phase, abort_flag, 6)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          if (!no_store) {
+            ptx::tmem_st_32x32b_x16(taddr, ra);
+            if constexpr (Cfg::kSfbGroups == 2) ptx::tmem_st_32x32b_x32(taddr + 16, rb);
+            else ptx::tmem_st_32x32b_x16(taddr + 16, rb);
+            ptx::tmem_st_wait();
+          }
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (ptx::elect_one()) {
+            if constexpr (kTwoCta) ptx::mbar_arrive_cluster(full_t);
+            else ptx::mbar_arrive(full_t);
+            // the stores above consumed every lane's registers, so the slot's bytes have
+            // certainly been read: hand it back to the scale loader
+            ptx::mbar_arrive(free_a);
+          }
+          if (tracing && q == 0 && lane == 0) trace_stamp(p, 3, iter, 1);
         }
-        // 2. registers -> this k-stage's tensor-memory buffer, once the MMAs of the k-stage that
-        //    used the buffer last (sf_depth k-stages ago) are done: their commit completes a
-        //    phase of that k-stage's `empty` barrier
-        if (need_lag && !ptx::mbar_wait(empty_bar + lag_stage, lag_phase, abort_flag, 6)) { ok = false; break; }
-        ptx::tc_fence_after_sync();
-        const uint32_t sf_taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                                  static_cast<uint32_t>(Cfg::kSfBase + sfbuf * Cfg::kSfColsPerBuf);
-        if (!(p.debug & 4)) {   // experiment switch: skip the tensor-memory stores
-        ptx::tmem_st_32x32b_x16(sf_taddr, ra);
-        if constexpr (Cfg::kSfbGroups == 2) ptx::tmem_st_32x32b_x32(sf_taddr + 16, rb);
-        else ptx::tmem_st_32x32b_x16(sf_taddr + 16, rb);
-        ptx::tmem_st_wait();
+        if (need_lag) {
+          lag_a += 8;
+          if (++lag_stage == kStages) { lag_stage = 0; lag_phase ^= 1; lag_a = empty_u32; }
         }
-        ptx::tc_fence_before_sync();
-        __syncwarp();
-        if (ptx::elect_one()) {
-          if (kTwoCta && !leader) ptx::mbar_arrive_remote(full_bar + stage, 0);
-          else ptx::mbar_arrive(full_bar + stage);
-          // the stores above consumed every lane's registers, so the slot's bytes have
-          // certainly been read: hand it back to the scale loader
-          ptx::mbar_arrive(sf_free_bar + slot);
-        }
-        if (q == 0 && lane == 0) trace_stamp(p, 3, iter, 1);
-        }
-        if (need_lag && ++lag_stage == kStages) { lag_stage = 0; lag_phase ^= 1; }
-        if (++slot == kSfSlots) { slot = 0; slot_phase ^= 1; }
+        src += Cfg::kSfSlotBytes; landed_a += 8; free_a += 8;
+        if (++slot == kSfSlots) { slot = 0; slot_phase ^= 1; src = sf_u32 + lane_off; landed_a = sf_landed_u32; free_a = sf_free_u32; }
         ++iter;
-        if (++sfbuf == sf_depth) sfbuf = 0;
-        if (++stage == kStages) stage = 0;
+        taddr += Cfg::kSfColsPerBuf;
+        if (++sfbuf == sf_depth) { sfbuf = 0; taddr = taddr0; }
+        full_t += 8;
+        if (++stage == kStages) { stage = 0; full_t = full_target_u32; }
       }
     }
   } else {

@@ -403,5 +403,149 @@ __host__ __device__ constexpr uint32_t make_idesc_nvfp4(int m, int n) {  // m = 
          (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// ------------------------------------------------ 32-bit shared-address variants
+//
+// The role loops of the GEMM kernel are chains of dependent scalar instructions; every
+// instruction on such a chain costs several cycles, so the loops keep barrier and buffer
+// addresses as 32-bit shared-window addresses that advance by an add per k-stage, instead of
+// generic pointers that need 64-bit arithmetic and a conversion before every use.
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+// Arrive on a barrier given by its shared::cluster address (this or another CTA of the cluster).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait (see mbar_wait above). The common case - the phase is already complete - is a
+// single non-blocking probe, which returns in less than half the time of try_wait.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (mbar_test_wait(bar, parity)) return true;
+  long long start = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 255u) == 0) {
+      if (*abort_flag != 0) return false;
+      if (clock64() - start > (1ll << 31)) {
+        atomicCAS(const_cast<int*>(abort_flag), 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void* desc, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_dst),
+      "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const void* desc, uint32_t bar_cluster_addr,
+                                                 int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_dst),
+      "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gmem_src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_dst),
+      "l"(reinterpret_cast<uint64_t>(gmem_src)), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+template <int kCtas>
+__device__ __forceinline__ void tc_commit(uint32_t bar, uint16_t cta_mask = 1) {
+  if constexpr (kCtas == 2)
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+        "[%0], %1;" ::"r"(bar), "h"(cta_mask)
+        : "memory");
+  else
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
+  return r;
+}
+
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+// Block-scaled MMA whose shared-memory descriptors are given as their low words (start address
+// and leading-dimension offset) plus one high word common to both (stride offset, version,
+// swizzle): advancing along K or to the next stage is a 32-bit add on the low word.
+template <int kCtas>
+__device__ __forceinline__ void tc_mma_nvfp4(uint32_t tmem_d, uint32_t desc_a_lo, uint32_t desc_b_lo,
+                                             uint32_t desc_hi, uint32_t idesc, uint32_t tmem_sfa,
+                                             uint32_t tmem_sfb, uint32_t accumulate) {
+  if constexpr (kCtas == 2)
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], da, db, %4, [%6], [%7], "
+        "p;\n\t}" ::"r"(tmem_d),
+        "r"(desc_a_lo), "r"(desc_b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], da, db, %4, [%6], [%7], "
+        "p;\n\t}" ::"r"(tmem_d),
+        "r"(desc_a_lo), "r"(desc_b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
+
+// Low / high words of the K-major 128-byte-swizzle descriptor (make_kmajor_sw128_desc).
+__device__ __forceinline__ uint32_t kmajor_sw128_desc_lo(uint32_t smem_addr) {
+  return ((smem_addr >> 4) & 0x3fffu) | ((16u >> 4) << 16);
+}
+constexpr uint32_t kKmajorSw128DescHi = ((1024u >> 4) & 0x3fffu) | (1u << 14) | (2u << 29);
+
 }  // namespace ptx
 }  // namespace b200
