@@ -108,6 +108,7 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   p.sfa = static_cast<const uint8_t*>(s.sfa);
   p.sfb = static_cast<const uint8_t*>(s.sfb);
   p.sfa_group_stride = s.sfa_group_stride;
+  p.sfa_atom_rows = static_cast<int>(s.sfa_group_stride / (static_cast<long long>(scale_k_padded(s.k)) * 128));
   p.sfb_group_stride = s.sfb_group_stride;
   p.b_group_rows = s.b_group_rows;
   p.out = s.out;
@@ -189,7 +190,7 @@ int pick_tile(const LaunchSpec& s, const DeviceInfo& dev) {
   // a pair tile is 256 rows tall: groups much shorter than that would leave half of every
   // pair idle, and such shapes are bound by streaming the weights anyway
   const bool tall_groups = s.avg_group_rows >= 384;
-  if (!s.out_f32 && splits == 1 && tall_groups && s.seqlens == nullptr &&
+  if (!s.out_f32 && splits == 1 && tall_groups &&
       ((mt + 1) / 2) * ((s.n + 255) / 256) >= dev.sm_count / 2)
     return 512;
   if (tasks(256) >= dev.sm_count * 2 / 3) return 256;
@@ -203,11 +204,6 @@ int launch_gemm(const LaunchSpec& s, cudaStream_t stream, int force_tile = 0) {
   if (!device_supported(dev)) return B200_NVFP4_UNSUPPORTED_DEVICE;
   int tile = force_tile ? force_tile : pick_tile(s, dev);
   if (tile == 512 && s.out_f32) tile = 256;
-  // The CTA-pair tile is used for dense and batched problems only. On expert-grouped problems
-  // with ragged groups it gave run-to-run differences (whole 32 x 64 output boxes of a worker's
-  // first tile) under a cold-cache stress and one launch failure; until that is understood,
-  // grouped problems run on single-CTA tiles, which pass the same stress.
-  if (tile == 512 && s.seqlens != nullptr) tile = 256;
   switch (tile) {
     case 512:
       return launch_instance<256, false, true>(s, dev, stream);

@@ -76,6 +76,7 @@ struct GemmParams {
   const int* cu_seqlens;      // [G+1] first row of each group (device) or nullptr
   const uint8_t* sfa;
   const uint8_t* sfb;
+  int sfa_atom_rows;          // 128-row atom rows in one group's SFA region
   long long sfa_group_stride;  // bytes between the scale regions of consecutive groups
   long long sfb_group_stride;
   int b_group_rows;           // rows of B per group (N), 0 when every group shares one B
@@ -405,8 +406,13 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (sf_tile0 + sfb_groups > n_sf_tiles) sfb_groups = n_sf_tiles - sf_tile0;
         const int ks_begin = (k_stages * t.split) / p.num_splits;
         const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
+        // A slab that lies wholly behind the group's scale region (second CTA of a pair on a short
+        // group or matrix) has no scales of its own; its rows are never stored, so it reads the
+        // region's last atom row instead of memory past the region.
+        int sfa_row = t.mt * kCtas + static_cast<int>(cta_rank);
+        if (sfa_row >= p.sfa_atom_rows) sfa_row = p.sfa_atom_rows - 1;
         const uint8_t* sfa_src = p.sfa + t.g * p.sfa_group_stride +
-                                 (static_cast<long long>(t.mt * kCtas + static_cast<int>(cta_rank)) * kt + ks_begin * 4) * kAtomBytes;
+                                 (static_cast<long long>(sfa_row) * kt + ks_begin * 4) * kAtomBytes;
         const uint8_t* sfb_src = p.sfb + t.g * p.sfb_group_stride +
                                  (static_cast<long long>(sf_tile0) * kt + ks_begin * 4) * kAtomBytes;
         const long long sfb_group_step = static_cast<long long>(kt) * kAtomBytes;
@@ -540,10 +546,16 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const bool mine = (iter & (kSfMoverTeams - 1)) == team;
         const bool need_lag = ahead >= sf_depth;
         if (!need_lag) ++ahead;
+        // Both teams wait for every k-stage's atoms, also the ones the other team moves: a
+        // parity wait is only meaningful for a waiter that has seen the previous phase of the
+        // same barrier complete. A team that looked at a slot's barrier only on its own turns
+        // would, with an odd number of slots, skip every other phase, and when it ran ahead of
+        // the other team it would take the older completed phase for the one it waits for (stale
+        // scales, and a fifth arrival on a four-arrival `sf_free` phase).
+        if (!ptx::mbar_wait(landed_a, slot_phase, abort_flag, 5)) { ok = false; break; }
         if (mine) {
           // 1. atoms of this k-stage: shared memory -> registers. Every lane polls: a
           //    single-lane wait costs a vote and a broadcast per call.
-          if (!ptx::mbar_wait(landed_a, slot_phase, abort_flag, 5)) { ok = false; break; }
           if (tracing && q == 0 && lane == 0) trace_stamp(p, 3, iter, 0);
           const int atoms = ks < k_stages_full ? 4 : kt - ks * 4;
           uint32_t ra[16];

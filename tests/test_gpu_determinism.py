@@ -37,7 +37,7 @@ def _repeat(fn, reps, junk):
                         f"columns {int(cols[0])}..{int(cols[-1])}")
 
 
-@pytest.mark.parametrize("tile_n", [0, 128])
+@pytest.mark.parametrize("tile_n", [0, 128, 512])
 def test_grouped_gemm_is_deterministic(ops, tile_n):
     from sm120_nvfp4_b200 import _lib
     _lib.lib().b200_nvfp4_set_tile_n(tile_n)
@@ -54,7 +54,7 @@ def test_grouped_gemm_is_deterministic(ops, tile_n):
     _repeat(lambda: ops.grouped_gemm(x, w, dc, dcu, xs, ws), 120, junk)
 
 
-@pytest.mark.parametrize("tile_n", [0, 256])
+@pytest.mark.parametrize("tile_n", [0, 256, 64])
 def test_dense_gemm_is_deterministic(ops, tile_n):
     from sm120_nvfp4_b200 import _lib
     _lib.lib().b200_nvfp4_set_tile_n(tile_n)
