@@ -316,11 +316,10 @@ class MoeWorkload:
         self.gw, self.gws = weights(2 * inter, hidden)
         self.dw, self.dws = weights(hidden, inter)
         self.x = torch.randn((tokens, hidden), device=device, generator=g).to(torch.bfloat16)
-        logits = torch.randn((tokens, experts), device=device, generator=g)
-        scores = torch.sigmoid(logits)
-        top = torch.topk(scores, topk, dim=1)
-        self.ids = top.indices.to(torch.int32).contiguous()
-        self.w = (top.values / top.values.sum(1, keepdim=True)).float().contiguous()
+        # router logits; the router step itself (sigmoid, top-k, renormalised weights) runs inside
+        # every timed step, in this library's kernel
+        self.logits = torch.randn((tokens, experts), device=device, generator=g)
+        self.ids, self.w = ops.router_topk(self.logits, topk)
         self.seq1 = torch.tensor([tokens], dtype=torch.int32, device=device)
         self.cu1 = torch.tensor([0, tokens], dtype=torch.int32, device=device)
         self.in_pad = (tokens + 127) // 128 * 128
@@ -338,6 +337,7 @@ class MoeWorkload:
         self.bytes_rank = w_bytes + sf_bytes + act
 
     def step(self):
+        self.ids, self.w = self.ops.router_topk(self.logits, self.k)
         if self.world == 1:
             packed, scales = self.ops.quantize_expert(self.x, self.seq1, self.cu1, scale_m_pad=self.in_pad)
             self.out = self.ops.fused_moe(packed, scales.flatten(), self.gw, self.gws, self.dw, self.dws, self.ids, self.w)
@@ -346,17 +346,15 @@ class MoeWorkload:
 
     def prepare_e2e(self):
         self.hx = torch.empty(self.x.shape, dtype=self.x.dtype).pin_memory().copy_(self.x.cpu())
-        self.hids = torch.empty(self.ids.shape, dtype=self.ids.dtype).pin_memory().copy_(self.ids.cpu())
-        self.hw = torch.empty(self.w.shape, dtype=self.w.dtype).pin_memory().copy_(self.w.cpu())
+        self.hlogits = torch.empty(self.logits.shape, dtype=self.logits.dtype).pin_memory().copy_(self.logits.cpu())
         self.step()
         self.hout = torch.empty(self.out.shape, dtype=self.out.dtype).pin_memory()
-        self.h2d = sum(t.numel() * t.element_size() for t in (self.hx, self.hids, self.hw))
+        self.h2d = sum(t.numel() * t.element_size() for t in (self.hx, self.hlogits))
         self.d2h = self.hout.numel() * self.hout.element_size()
 
     def step_e2e(self):
         self.x.copy_(self.hx, non_blocking=True)
-        self.ids.copy_(self.hids, non_blocking=True)
-        self.w.copy_(self.hw, non_blocking=True)
+        self.logits.copy_(self.hlogits, non_blocking=True)
         self.step()
         self.hout.copy_(self.out, non_blocking=True)
 

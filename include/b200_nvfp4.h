@@ -226,6 +226,14 @@ B200_NVFP4_API int b200_nvfp4_expert_moe(void* output, const void* input, const 
                                          int num_expert_local, int grouped_scale_m_pad,
                                          b200_stream_t stream);
 
+/* Router step in front of the routed layer (no counterpart in the reference library, whose
+ * entry points take topk_ids / topk_weights as inputs): logits FP32 [T, E] -> sigmoid scores,
+ * the num_topk largest per token (ties to the lower expert id) as int32 ids [T, k], and FP32
+ * weights [T, k] = score / sum of the selected scores. E <= 4096. */
+B200_NVFP4_API int b200_nvfp4_moe_router_topk(const void* logits, void* topk_ids,
+                                              void* topk_weights, int num_tokens, int num_experts,
+                                              int num_topk, b200_stream_t stream);
+
 /* Expert-parallel hand-off (no counterpart in the reference library; its hand-off benchmark
  * benchmarks/integration/benchmark_deepep_handoff.py:356-364 ships one BF16 row per
  * (token, expert) with torch ops). A token is sent once to each rank that owns one of its

@@ -62,7 +62,7 @@ def lib():
         for name in ("oracle_quantize_rows_f32", "oracle_gemm_sampled", "oracle_gemm",
                      "oracle_grouped_gemm", "oracle_splitk_reduce", "oracle_count_and_gather",
                      "oracle_act_mul_and_quant", "oracle_quantize_expert", "oracle_reduce",
-                     "oracle_expert_moe", "oracle_fused_moe"):
+                     "oracle_expert_moe", "oracle_fused_moe", "oracle_router_topk"):
             getattr(L, name).restype = None
         _lib = L
     return _lib
@@ -273,6 +273,15 @@ def fused_moe(x, x_scale, gate_up_w, gate_up_ws, down_w, down_ws, topk_ids, topk
                            _p(w, f32p), _p(shared, u16p), t, hidden, inter, topk, e, rank_ep,
                            in_m_pad, _p(pos, i32p), _p(seqlens, i32p), _p(cu, i32p))
     return out.view(np.float16), pos, seqlens, cu
+
+
+def router_topk(logits, num_topk: int):
+    logits = _c(logits, np.float32)
+    t, e = logits.shape
+    ids = np.empty((t, num_topk), np.int32)
+    w = np.empty((t, num_topk), np.float32)
+    lib().oracle_router_topk(_p(ids, i32p), _p(w, f32p), _p(logits, f32p), t, e, num_topk)
+    return ids, w
 
 
 E2M1_LEVELS = np.array([0., .5, 1., 1.5, 2., 3., 4., 6., -0., -.5, -1., -1.5, -2., -3., -4., -6.],

@@ -589,6 +589,38 @@ ORACLE_API void oracle_fused_moe(uint16_t *output, const uint8_t *input,
   free(down_out);
 }
 
+/* Router step in front of the fused MoE. The reference library has no such function (its
+ * entry points take topk_ids / topk_weights as inputs; its tests build them by hand,
+ * tests/python/test_fused_moe.py:60-75); the DeepSeek-shaped configuration defines it: sigmoid
+ * scores, the num_topk largest per token (ties to the lower expert id), weights = score / sum of
+ * the selected scores. score = 1 / (1 + exp(-logit)) with oracle_expf, the sum taken in
+ * selection order - the operation sequence of the CUDA kernel. */
+ORACLE_API void oracle_router_topk(int *topk_ids, float *topk_weights, const float *logits,
+                                   int num_tokens, int num_experts, int num_topk) {
+  int t;
+#pragma omp parallel for schedule(static)
+  for (t = 0; t < num_tokens; ++t) {
+    float *score = (float *)malloc((size_t)num_experts * sizeof(float));
+    float sum = 0.0f;
+    int e, r;
+    for (e = 0; e < num_experts; ++e)
+      score[e] = 1.0f / (1.0f + oracle_expf(-logits[(int64_t)t * num_experts + e]));
+    for (r = 0; r < num_topk; ++r) {
+      int best = -1;
+      for (e = 0; e < num_experts; ++e)
+        if (score[e] >= 0.0f && (best < 0 || score[e] > score[best])) best = e;
+      topk_ids[t * num_topk + r] = best;
+      topk_weights[t * num_topk + r] = best >= 0 ? score[best] : 0.0f;
+      if (best >= 0) {
+        sum = r == 0 ? score[best] : sum + score[best];
+        score[best] = -1.0f;
+      }
+    }
+    for (r = 0; r < num_topk; ++r) topk_weights[t * num_topk + r] = topk_weights[t * num_topk + r] / sum;
+    free(score);
+  }
+}
+
 /* src/fused_moe/fused_moe.cu:76-95 and python/sm120_nvfp4/__init__.py:245-269 */
 ORACLE_API uint64_t oracle_expert_moe_workspace_size(int total_rows, int hidden, int inter,
                                                      int num_expert_local, int m_scale_pad) {

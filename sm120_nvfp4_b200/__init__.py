@@ -12,7 +12,8 @@ include/b200_nvfp4.h on torch's current stream. torch is used for memory and str
 from __future__ import annotations
 
 from .ops import (cute_gemm, cutlass_gemm, expert_moe, expert_moe_workspace_bytes, fused_moe, gemm,
-                  grouped_gemm, quantize_expert, scale_a_elements, scale_b_elements, scale_k_padded)
+                  grouped_gemm, pack_weights, quantize_expert, router_topk, scale_a_elements, scale_b_elements,
+                  scale_k_padded)
 
 __all__ = [
     "expert_moe",
@@ -26,4 +27,7 @@ __all__ = [
     "scale_k_padded",
     "scale_a_elements",
     "scale_b_elements",
+    # not in the reference package: the callers either side of the routed layer
+    "router_topk",
+    "pack_weights",
 ]

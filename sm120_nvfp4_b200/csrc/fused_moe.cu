@@ -216,6 +216,12 @@ int b200_nvfp4_fused_moe(void* output, const void* input, const void* input_scal
                          static_cast<cudaStream_t>(stream));
 }
 
+int b200_nvfp4_moe_router_topk(const void* logits, void* topk_ids, void* topk_weights,
+                               int num_tokens, int num_experts, int num_topk, b200_stream_t stream) {
+  return b200::moe_router_topk(logits, topk_ids, topk_weights, num_tokens, num_experts, num_topk,
+                               static_cast<cudaStream_t>(stream));
+}
+
 size_t b200_nvfp4_expert_moe_workspace_bytes(int total_rows, int hidden_size, int intermediate_size,
                                              int num_expert_local, int grouped_scale_m_pad) {
   (void)hidden_size;

@@ -46,6 +46,9 @@ int moe_route(const void* topk_ids, void* topk_pos, void* seqlens, void* cu_seql
 int moe_move_rows(void* dst, const void* src, const void* index, int count, int fanout, int row_bytes,
                   bool scatter, cudaStream_t stream);
 
+int moe_router_topk(const void* logits, void* topk_ids, void* topk_weights, int num_tokens,
+                    int num_experts, int num_topk, cudaStream_t stream);
+
 int moe_reduce(void* output, const void* down_output, const void* topk_pos, const void* topk_scale,
                const void* shared_output, int num_tokens, int hidden_size, int num_topk,
                bool out_is_bf16, cudaStream_t stream);

@@ -378,6 +378,67 @@ reduce_kernel(void* __restrict__ output, const __half* __restrict__ down_output,
   }
 }
 
+// ------------------------------------------------------------------------- router
+//
+// Router step in front of the routed layer: score = sigmoid(logit), the num_topk largest per
+// token (ties to the lower expert id), weight = score / sum of the selected scores (sum in
+// selection order). The reference library leaves this step to its caller. One warp per token:
+// the scores sit in shared memory, every round each lane scans its strided share and the warp
+// agrees on the best (score, lowest id) with shuffles.
+__global__ void __launch_bounds__(256)
+router_topk_kernel(const float* __restrict__ logits, int* __restrict__ topk_ids,
+                   float* __restrict__ topk_weights, int num_tokens, int num_experts, int num_topk) {
+  extern __shared__ float s_scores[];
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  float* score = s_scores + static_cast<size_t>(threadIdx.x >> 5) * num_experts;
+  for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < num_tokens; t += gridDim.x * warps_per_block) {
+    const float* row = logits + static_cast<long long>(t) * num_experts;
+    for (int e = lane; e < num_experts; e += 32)
+      score[e] = __fdiv_rn(1.0f, __fadd_rn(1.0f, nvfp4_expf(-row[e])));
+    __syncwarp();
+    float sum = 0.0f;
+    float my_weight = 0.0f;   // lane r keeps the score of rank r (num_topk <= 32 per pass)
+    int my_id = -1;
+    for (int r = 0; r < num_topk; ++r) {
+      float best = -1.0f;
+      int best_id = 0x7fffffff;
+      for (int e = lane; e < num_experts; e += 32) {
+        const float v = score[e];
+        if (v > best) { best = v; best_id = e; }   // ascending e: the first maximum has the lowest id
+      }
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, d);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_id, d);
+        if (ov > best || (ov == best && oi < best_id)) { best = ov; best_id = oi; }
+      }
+      const bool found = best >= 0.0f;
+      if (found) {
+        sum = r == 0 ? best : __fadd_rn(sum, best);
+        if (lane == 0) score[best_id] = -1.0f;
+      }
+      if ((r & 31) == lane) { my_weight = found ? best : 0.0f; my_id = found ? best_id : -1; }
+      __syncwarp();
+      if ((r & 31) == 31 || r == num_topk - 1) {
+        // flush up to 32 selections; the divisor needs the complete sum, so weights are
+        // normalised in a second pass below
+        const int base = r & ~31;
+        if (base + lane <= r) {
+          topk_ids[static_cast<long long>(t) * num_topk + base + lane] = my_id;
+          topk_weights[static_cast<long long>(t) * num_topk + base + lane] = my_weight;
+        }
+      }
+    }
+    __syncwarp();
+    for (int r = lane; r < num_topk; r += 32) {
+      float* w = topk_weights + static_cast<long long>(t) * num_topk + r;
+      *w = __fdiv_rn(*w, sum);
+    }
+    __syncwarp();
+  }
+}
+
 __global__ void __launch_bounds__(256)
 move_rows_kernel(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src,
                  const int* __restrict__ index, int count, int fanout, int row_bytes, bool scatter) {
@@ -562,6 +623,24 @@ int moe_move_rows(void* dst, const void* src, const void* index, int count, int 
   move_rows_kernel<<<blocks, 256, 0, stream>>>(static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src),
                                                static_cast<const int*>(index), count, fanout, row_bytes,
                                                scatter);
+  count_launch();
+  return check_launch();
+}
+
+int moe_router_topk(const void* logits, void* topk_ids, void* topk_weights, int num_tokens,
+                    int num_experts, int num_topk, cudaStream_t stream) {
+  if (logits == nullptr || topk_ids == nullptr || topk_weights == nullptr || num_tokens <= 0 ||
+      num_experts <= 0 || num_experts > 4096 || num_topk <= 0 || num_topk > num_experts) {
+    return B200_NVFP4_INVALID_ARGUMENT;
+  }
+  const DeviceInfo& dev = current_device_info();
+  if (!dev.ok) return B200_NVFP4_CUDA_ERROR;
+  int blocks = (num_tokens + 7) / 8;
+  const int max_blocks = dev.sm_count * 8;
+  if (blocks > max_blocks) blocks = max_blocks;
+  router_topk_kernel<<<blocks, 256, static_cast<size_t>(8) * num_experts * sizeof(float), stream>>>(
+      static_cast<const float*>(logits), static_cast<int*>(topk_ids), static_cast<float*>(topk_weights),
+      num_tokens, num_experts, num_topk);
   count_launch();
   return check_launch();
 }

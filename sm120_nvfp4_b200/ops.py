@@ -477,3 +477,45 @@ _LIBRARY.impl("grouped_gemm", _grouped_impl, "CUDA")
 _LIBRARY.impl("fused_moe", _fused_impl, "CUDA")
 _LIBRARY.impl("quantize_expert", _quant_impl, "CUDA")
 _LIBRARY.impl("expert_moe", _expert_impl, "CUDA")
+
+
+# ------------------------------------------------------------------------------------------
+# Callers either side of the routed layer. Neither exists in the reference package (its router
+# step and its weight conversion are left to the caller); both run this library's CUDA kernels.
+
+def router_topk(logits: torch.Tensor, num_topk: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Router step: FP32 logits [T, E] -> (topk_ids int32 [T, k], topk_weights float32 [T, k]).
+
+    score = sigmoid(logit); the k largest per token, ties to the lower expert id; weights are the
+    selected scores divided by their sum. The outputs are what fused_moe takes as topk_ids /
+    topk_weights.
+    """
+    _check(logits.is_cuda and logits.dim() == 2 and logits.dtype == torch.float32 and logits.is_contiguous(),
+           "logits must be a contiguous float32 CUDA tensor [num_tokens, num_experts]")
+    t, e = logits.shape
+    _check(t > 0 and 0 < num_topk <= e <= 4096, "need num_tokens > 0 and 0 < num_topk <= num_experts <= 4096")
+    ids = torch.empty((t, num_topk), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((t, num_topk), dtype=torch.float32, device=logits.device)
+    with torch.cuda.device(logits.device):
+        status = _lib.lib().b200_nvfp4_moe_router_topk(logits.data_ptr(), ids.data_ptr(), weights.data_ptr(), t, e,
+                                                       int(num_topk), _stream(logits.device))
+    _check(status == 0, f"router_topk launch failed: {_lib.status_string(status)}")
+    return ids, weights
+
+
+def pack_weights(weight: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """BF16 / FP16 expert weights [E, N, K] -> (packed E2M1 uint8 [E, N, K/2], UE4M3 scales uint8
+    [E, align128(N) * scale_k_padded(K)]) in the layout grouped_gemm / fused_moe expect for
+    `weight` / `weight_scale`: one UE4M3 scale = amax / 6 per 16 values of K, one 128-row-aligned
+    block-scaled region per expert. Uses the row quantiser of quantize_expert with one group per
+    expert.
+    """
+    _check(weight.is_cuda and weight.dim() == 3 and weight.dtype in (torch.bfloat16, torch.float16) and
+           weight.is_contiguous(), "weight must be a contiguous BF16/FP16 CUDA tensor [experts, N, K]")
+    e, n, k = weight.shape
+    _check(k % 32 == 0, "K must be a multiple of 32")
+    dev = weight.device
+    seqlens = torch.full((e,), n, dtype=torch.int32, device=dev)
+    cu = torch.arange(0, (e + 1) * n, n, dtype=torch.int32, device=dev)
+    packed, scales = quantize_expert(weight.view(e * n, k), seqlens, cu, scale_m_pad=(n + 127) // 128 * 128)
+    return packed.view(e, n, k // 2), scales

@@ -260,3 +260,35 @@ def test_full_moe_random_vs_oracle(ops, tokens, experts, topk, hidden, inter, ra
     num = np.linalg.norm(got.astype(np.float64) - want.astype(np.float64))
     den = np.linalg.norm(want.astype(np.float64))
     assert np.isfinite(got).all() and num / den < 2e-2, num / den
+
+
+@pytest.mark.parametrize("tokens,experts,topk", [(4096, 256, 8), (77, 8, 3), (5, 40, 40), (300, 1000, 6)])
+def test_router_topk_bit_exact(ops, tokens, experts, topk):
+    # sigmoid scores, top-k with ties to the lower id, renormalised weights: ids and weight bits
+    rng = np.random.default_rng(tokens + experts)
+    logits = rng.standard_normal((tokens, experts), dtype=np.float32)
+    logits[0, : min(experts, 6)] = 0.25          # ties
+    if tokens > 1:
+        logits[1, :] = -3.0                      # all equal
+    want_ids, want_w = oracle.router_topk(logits, topk)
+    ids, w = ops.router_topk(_dev(logits), topk)
+    np.testing.assert_array_equal(ids.cpu().numpy(), want_ids)
+    np.testing.assert_array_equal(w.cpu().numpy().view(np.uint32), want_w.view(np.uint32))
+    assert np.allclose(want_w.sum(1), 1.0, atol=1e-5)
+    assert (np.sort(want_ids, axis=1)[:, 1:] != np.sort(want_ids, axis=1)[:, :-1]).all()
+
+
+def test_pack_weights_matches_row_quantiser(ops):
+    experts, n, k = 3, 200, 256
+    rng = np.random.default_rng(9)
+    w = torch.from_numpy(rng.standard_normal((experts, n, k), dtype=np.float32) * 0.02).to(torch.bfloat16)
+    packed, scales = ops.pack_weights(w.cuda())
+    assert tuple(packed.shape) == (experts, n, k // 2) and tuple(scales.shape) == (experts, 256 * ops.scale_k_padded(k))
+    for e in range(experts):
+        pk, sc = oracle.quantize_rows(w[e].float().numpy())
+        np.testing.assert_array_equal(packed[e].cpu().numpy(), pk)
+        nkb = k // 16
+        r = np.repeat(np.arange(n, dtype=np.int32), nkb)
+        kb = np.tile(np.arange(nkb, dtype=np.int32), n)
+        off = oracle.sf_offsets(r, kb, k)
+        np.testing.assert_array_equal(scales[e].cpu().numpy()[off], sc[off])

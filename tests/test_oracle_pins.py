@@ -262,3 +262,20 @@ def test_expf_accuracy_against_libm():
     assert worst < 2.0, worst
     assert L.oracle_silu(0.0) == 0.0 and abs(L.oracle_silu(1.0) - 0.7310585786) < 1e-6
     assert L.oracle_silu(-200.0) == 0.0 or L.oracle_silu(-200.0) == -0.0
+
+
+def test_router_topk_against_numpy_restatement():
+    # the router of the DeepSeek-shaped configuration, restated with numpy: same ids wherever the
+    # float32 scores are distinct, weights equal to a few ulp
+    from helpers import topk_routing
+    rng = np.random.default_rng(12)
+    logits = rng.standard_normal((64, 256), dtype=np.float32)
+    ids, w = oracle.router_topk(logits, 8)
+    scores = 1.0 / (1.0 + np.exp(-logits.astype(np.float64)))
+    order = np.argsort(-scores, axis=1, kind="stable")[:, :8]
+    np.testing.assert_array_equal(ids, order.astype(np.int32))
+    picked = np.take_along_axis(scores, order, axis=1)
+    np.testing.assert_allclose(w, picked / picked.sum(1, keepdims=True), rtol=2e-6)
+    tie = np.zeros((1, 16), np.float32)
+    ids, w = oracle.router_topk(tie, 4)
+    assert ids.tolist() == [[0, 1, 2, 3]] and np.allclose(w, 0.25)
