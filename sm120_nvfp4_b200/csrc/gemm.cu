@@ -77,9 +77,16 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   });
   if (attr_status[dev.device] != cudaSuccess) return B200_NVFP4_CUDA_ERROR;
 
+  // Rows of A one load brings in: 128, or the whole (8-row padded) matrix when it is shorter. Only
+  // for a single dense problem: groups of a batch or of an expert layout follow each other in
+  // memory and tiles address them by row offset.
+  int a_box_rows = kBlockM;
+  if (!kTwoCta && s.seqlens == nullptr && s.num_groups == 1 && s.m_uniform < kBlockM)
+    a_box_rows = (s.m_uniform + 7) / 8 * 8;
+  const int a_sub_bytes = a_box_rows * kStageKBytes;
   CUtensorMap tmap_a, tmap_b;
   const uint64_t row_bytes = static_cast<uint64_t>(s.k) / 2;
-  if (!encode_tmap_2d_u8(&tmap_a, s.a, static_cast<uint64_t>(s.a_rows_total), row_bytes, kBlockM,
+  if (!encode_tmap_2d_u8(&tmap_a, s.a, static_cast<uint64_t>(s.a_rows_total), row_bytes, a_box_rows,
                          kStageKBytes, CU_TENSOR_MAP_SWIZZLE_128B) ||
       !encode_tmap_2d_u8(&tmap_b, s.b, static_cast<uint64_t>(s.b_rows_total), row_bytes,
                          Cfg::kBRows, kStageKBytes, CU_TENSOR_MAP_SWIZZLE_128B)) {
@@ -119,8 +126,9 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   p.tiles_out = s.tiles_out;
   p.cu_tiles_out = s.cu_tiles_out;
   p.error = device_error_word();
-  p.num_stages = Cfg::stages_for(s.num_groups);
-  p.num_sf_slots = Cfg::sf_slots_for(s.num_groups);
+  p.a_sub_bytes = a_sub_bytes;
+  p.num_stages = Cfg::stages_for(s.num_groups, a_sub_bytes);
+  p.num_sf_slots = Cfg::sf_slots_for(s.num_groups, a_sub_bytes);
   static const int debug_flags = [] { const char* e = std::getenv("B200_NVFP4_DEBUG"); return e ? std::atoi(e) : 0; }();
   p.debug = debug_flags;
   p.trace = nullptr;
@@ -160,7 +168,7 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(static_cast<unsigned>(workers * Cfg::kCtas));
   config.blockDim = dim3(kGemmThreads);
-  config.dynamicSmemBytes = Cfg::smem_bytes(s.num_groups);
+  config.dynamicSmemBytes = Cfg::smem_bytes(s.num_groups, a_sub_bytes);
   config.stream = stream;
   cudaLaunchAttribute attrs[1];
   attrs[0].id = cudaLaunchAttributeClusterDimension;

@@ -88,6 +88,7 @@ struct GemmParams {
   int* tiles_out;             // optional [G]   ceil(rows/128) per group
   int* cu_tiles_out;          // optional [G+1] exclusive prefix of tiles_out
   int* error;                 // device word that receives a non-zero code on a timed-out wait
+  int a_sub_bytes;            // shared-memory bytes of one sub-stage of A: rows in the A box x 128
   int num_stages;             // depth of the operand ring in shared memory (<= kMaxStages)
   int num_sf_slots;           // depth of the scale-atom ring in shared memory (<= kMaxSfSlots)
   int tma_store;              // 1: the output tensor map is valid, full 32-row slabs go out by TMA store
@@ -113,16 +114,29 @@ struct GemmCfg {
   // k-stage in flight, so the scale copies of a k-stage can be issued (by their own warps)
   // while the MMAs of earlier stages are still running. The ring is as deep as the columns
   // allow, but never deeper than the operand ring (kernel: sf_depth).
-  static constexpr int kSfColsPerBuf = 16 + 4 * kSfbColsPerMma;   // 4 MMAs: SFA 4x4, SFB 4xN/32
+  // Sub-stages per pipeline stage. One sub-stage is 256 k-values (one 128-byte swizzle span, four
+  // MMAs). A barrier round - waits, arrivals, commit, the scale movers' pass - costs several
+  // hundred cycles whatever it carries, and an MMA costs its issuing thread ~50 cycles however
+  // narrow it is; for 64-column tiles (skinny problems, bound by streaming B) two sub-stages per
+  // round halve the rounds per byte.
+  static constexpr int kSub = BN == 64 ? 2 : 1;
+  static constexpr int kAtomsPerStage = 4 * kSub;
+  static constexpr int kSfColsPerSub = 16 + 4 * kSfbColsPerMma;   // 4 MMAs: SFA 4x4, SFB 4xN/32
+  static constexpr int kSfColsPerBuf = kSub * kSfColsPerSub;
   static constexpr int kSfBase = kAccStages * BN;
   static constexpr int kMaxSfBufs = (512 - kSfBase) / kSfColsPerBuf;
   static constexpr int kTmemCols = 512;
+  // One sub-stage of A: 128 rows, or fewer when the whole problem has fewer rows (the loader's box
+  // then covers round-up-to-8 rows; the MMA still reads 128 rows' worth of shared memory, the rest
+  // being whatever follows - rows that are never stored). The freed space deepens the ring, which
+  // is what a skinny problem needs: it is bound by the bytes of B in flight.
   static constexpr int kABytes = kBlockM * kStageKBytes;
-  static constexpr int kBBytes = kBRows * kStageKBytes;
-  static constexpr int kSfaBytes = 4 * kAtomBytes;
+  static constexpr int kBBytes = kBRows * kStageKBytes;            // one sub-stage of B
+  static constexpr int kSfaBytes = 4 * kAtomBytes;                 // one sub-stage of SFA atoms
   static constexpr int kSfbBytes = kSfbGroups * 4 * kAtomBytes;
-  static constexpr int kStageBytes = kABytes + kBBytes;       // one stage of the operand ring
-  static constexpr int kSfSlotBytes = kSfaBytes + kSfbBytes;  // one slot of the scale-atom ring
+  // stage layout: [A sub-stages][B sub-stages]; slot layout: [SFA atoms][SFB atoms of group 0][group 1]
+  __host__ __device__ static constexpr int stage_bytes(int a_sub_bytes) { return kSub * (a_sub_bytes + kBBytes); }
+  static constexpr int kSfSlotBytes = kSub * (kSfaBytes + kSfbBytes);  // one slot of the scale-atom ring
   // Output staging for TMA stores: 32 rows x 128 bytes per epilogue warp. Tiles of 64 columns
   // give a warp only 32 columns (64 bytes of FP16 per row) and keep the direct-store epilogue.
   static constexpr int kStagingWarpBytes = 32 * 128;
@@ -136,18 +150,20 @@ struct GemmCfg {
     return 1024 + kBarrierBytes + 3 * (num_groups + 1) * 4 + kStagingBytes;
   }
   static constexpr int kMinSfSlots = 4;
-  static constexpr int stages_for(int num_groups) {
-    // as many operand stages as fit beside a minimum of scale slots
-    int s = (kSmemBudget - fixed_bytes(num_groups) - kMinSfSlots * kSfSlotBytes) / kStageBytes;
+  static constexpr int stages_for(int num_groups, int a_sub_bytes = kABytes) {
+    // as many operand stages as fit beside a minimum of scale slots; the MMA reads a full 128-row
+    // A block from the last sub-stage, so that much shared memory must follow it
+    int s = (kSmemBudget - fixed_bytes(num_groups) - kMinSfSlots * kSfSlotBytes) / stage_bytes(a_sub_bytes);
     return s > kMaxStages ? kMaxStages : s;
   }
-  static constexpr int sf_slots_for(int num_groups) {
-    int n = (kSmemBudget - fixed_bytes(num_groups) - stages_for(num_groups) * kStageBytes) / kSfSlotBytes;
+  static constexpr int sf_slots_for(int num_groups, int a_sub_bytes = kABytes) {
+    int n = (kSmemBudget - fixed_bytes(num_groups) - stages_for(num_groups, a_sub_bytes) * stage_bytes(a_sub_bytes)) /
+            kSfSlotBytes;
     return n > kMaxSfSlots ? kMaxSfSlots : n;
   }
-  static constexpr int smem_bytes(int num_groups) {
-    return fixed_bytes(num_groups) + stages_for(num_groups) * kStageBytes +
-           sf_slots_for(num_groups) * kSfSlotBytes;
+  static constexpr int smem_bytes(int num_groups, int a_sub_bytes = kABytes) {
+    return fixed_bytes(num_groups) + stages_for(num_groups, a_sub_bytes) * stage_bytes(a_sub_bytes) +
+           sf_slots_for(num_groups, a_sub_bytes) * kSfSlotBytes;
   }
   static_assert(stages_for(kMaxGroups) >= 3, "pipeline too shallow");
 };
@@ -201,6 +217,12 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
   using Cfg = GemmCfg<BN, kTwoCta>;
+  if ((p.debug & 64) && p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long ns;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+    p.trace[((0 * 8 + 7) * 64 + 61) * 2 + 0] = static_cast<unsigned long long>(clock64());
+    p.trace[((0 * 8 + 7) * 64 + 61) * 2 + 1] = ns;
+  }
   constexpr int kCtas = Cfg::kCtas;
   constexpr int kAccStages = Cfg::kAccStages;
   constexpr int kTileM = Cfg::kTileM;
@@ -215,7 +237,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* stage_base = smem;
   const int kSfSlots = p.num_sf_slots;
-  uint8_t* staging_base = smem + kStages * Cfg::kStageBytes;   // 1024-byte aligned: stages are multiples of 1 KB
+  const uint32_t a_bytes = static_cast<uint32_t>(p.a_sub_bytes);
+  const uint32_t stage_bytes = static_cast<uint32_t>(Cfg::stage_bytes(p.a_sub_bytes));
+  uint8_t* staging_base = smem + kStages * stage_bytes;   // 1024-byte aligned: stages are multiples of 1 KB
   uint8_t* sf_base = staging_base + Cfg::kStagingBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(sf_base + kSfSlots * Cfg::kSfSlotBytes);
   // full:      the stage is ready for the MMAs: its A / B tiles landed in shared memory and
@@ -256,63 +280,82 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     s_row0[g] = p.cu_seqlens ? p.cu_seqlens[g] : g * p.m_uniform;
     s_cu_tiles[g] = (rows + kTileM - 1) / kTileM;
   }
-  if (threadIdx.x == 0) {
-    *abort_flag = 0;
-    for (int s = 0; s < kStages; ++s) {
-      // arrivals: the A and the B loader of the owning CTA + every scale-mover warp
+  // Set-up runs in parallel: the lanes of warp 0 initialise one barrier each, the MMA warp
+  // allocates tensor memory meanwhile. A single problem (one group) needs no scan of tile counts
+  // and therefore only one block-wide barrier before the pipeline starts.
+  if (warp == 0) {
+    if (lane == 0) *abort_flag = 0;
+    for (int s = lane; s < kStages; s += 32) {
+      // arrivals: the A and the B loader of the owning CTA + every scale-mover warp of a team
       ptx::mbar_init(full_bar + s, 2 + 4 * kCtas);
       ptx::mbar_init(empty_bar + s, 1);
     }
-    for (int s = 0; s < kSfSlots; ++s) {
+    for (int s = lane; s < kSfSlots; s += 32) {
       ptx::mbar_init(sf_landed_bar + s, 1);
       ptx::mbar_init(sf_free_bar + s, 4);
     }
-    for (int s = 0; s < 2; ++s) {
-      ptx::mbar_init(acc_full_bar + s, 1);
-      ptx::mbar_init(acc_empty_bar + s, kEpilogueWarps * kCtas);
+    if (lane < 2) {
+      ptx::mbar_init(acc_full_bar + lane, 1);
+      ptx::mbar_init(acc_empty_bar + lane, kEpilogueWarps * kCtas);
     }
-    ptx::fence_barrier_init();
-    ptx::prefetch_tensormap(&tmap_a);
-    ptx::prefetch_tensormap(&tmap_b);
-    if (p.tma_store) ptx::prefetch_tensormap(&tmap_out);
+    __syncwarp();
+    if (lane == 0) {
+      ptx::fence_barrier_init();
+      ptx::prefetch_tensormap(&tmap_a);
+      ptx::prefetch_tensormap(&tmap_b);
+      if (p.tma_store) ptx::prefetch_tensormap(&tmap_out);
+    }
+  } else if (warp == kWarpMma) {
+    ptx::tmem_alloc<kCtas>(tmem_holder, Cfg::kTmemCols);
+    ptx::tmem_relinquish<kCtas>();
   }
-  __syncthreads();
-  if (warp == kWarpLoadA) {  // exclusive scan of the per-group tile counts, 32 groups at a time
-    int carry = 0;
-    for (int base = 0; base < G; base += 32) {
-      int v = (base + lane < G) ? s_cu_tiles[base + lane] : 0;
-      int incl = v;
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        int o = __shfl_up_sync(0xffffffffu, incl, d);
-        if (lane >= d) incl += o;
+  if (G == 1) {
+    if (threadIdx.x == 0) {   // this thread wrote the only table entry itself
+      const int tiles = s_cu_tiles[0];
+      s_cu_tiles[0] = 0;
+      s_cu_tiles[1] = tiles;
+      if (blockIdx.x == 0) {
+        const int t128 = (s_rows[0] + kBlockM - 1) / kBlockM;
+        if (p.tiles_out) p.tiles_out[0] = t128;
+        if (p.cu_tiles_out) { p.cu_tiles_out[0] = 0; p.cu_tiles_out[1] = t128; }
       }
-      if (base + lane < G) s_cu_tiles[base + lane] = carry + incl - v;
-      carry += __shfl_sync(0xffffffffu, incl, 31);
     }
-    if (lane == 0) s_cu_tiles[G] = carry;
-    if (blockIdx.x == 0 && (p.tiles_out || p.cu_tiles_out)) {
-      // the reference ABI's scratch outputs: 128-row tile count per group and its prefix
-      int run = 0;
+  } else {
+    __syncthreads();
+    if (warp == kWarpLoadA) {  // exclusive scan of the per-group tile counts, 32 groups at a time
+      int carry = 0;
       for (int base = 0; base < G; base += 32) {
-        int v = (base + lane < G) ? (s_rows[base + lane] + kBlockM - 1) / kBlockM : 0;
+        int v = (base + lane < G) ? s_cu_tiles[base + lane] : 0;
         int incl = v;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
           int o = __shfl_up_sync(0xffffffffu, incl, d);
           if (lane >= d) incl += o;
         }
-        if (base + lane < G) {
-          if (p.tiles_out) p.tiles_out[base + lane] = v;
-          if (p.cu_tiles_out) p.cu_tiles_out[base + lane] = run + incl - v;
-        }
-        run += __shfl_sync(0xffffffffu, incl, 31);
+        if (base + lane < G) s_cu_tiles[base + lane] = carry + incl - v;
+        carry += __shfl_sync(0xffffffffu, incl, 31);
       }
-      if (lane == 0 && p.cu_tiles_out) p.cu_tiles_out[G] = run;
+      if (lane == 0) s_cu_tiles[G] = carry;
+      if (blockIdx.x == 0 && (p.tiles_out || p.cu_tiles_out)) {
+        // the reference ABI's scratch outputs: 128-row tile count per group and its prefix
+        int run = 0;
+        for (int base = 0; base < G; base += 32) {
+          int v = (base + lane < G) ? (s_rows[base + lane] + kBlockM - 1) / kBlockM : 0;
+          int incl = v;
+#pragma unroll
+          for (int d = 1; d < 32; d <<= 1) {
+            int o = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += o;
+          }
+          if (base + lane < G) {
+            if (p.tiles_out) p.tiles_out[base + lane] = v;
+            if (p.cu_tiles_out) p.cu_tiles_out[base + lane] = run + incl - v;
+          }
+          run += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0 && p.cu_tiles_out) p.cu_tiles_out[G] = run;
+      }
     }
-  } else if (warp == kWarpMma) {
-    ptx::tmem_alloc<kCtas>(tmem_holder, Cfg::kTmemCols);
-    ptx::tmem_relinquish<kCtas>();
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
@@ -330,7 +373,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int n_tiles = (p.n + BN - 1) / BN;
   const int total_tasks = total_mt * n_tiles * p.num_splits;
   const int kt = (p.k + 63) / 64;               // scale atoms along K
-  const int k_stages = (kt + 3) / 4;            // pipeline stages along K
+  constexpr int kSub = Cfg::kSub;
+  constexpr int kAtomsPerStage = Cfg::kAtomsPerStage;
+  const int k_stages = (kt + kAtomsPerStage - 1) / kAtomsPerStage;   // pipeline stages along K
   const int n_sf_tiles = (p.n + 127) / 128;     // 128-row scale tiles of B
 
   // 32-bit shared-window addresses of the rings: the role loops below advance them with adds.
@@ -343,7 +388,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // where arrivals for a stage's `full` barrier go: this CTA's barrier, or the leader's
   const uint32_t full_target_u32 = kTwoCta ? ptx::map_to_cta(full_u32, 0) : full_u32;
   const bool tracing = (p.debug & 64) != 0 && p.trace != nullptr && blockIdx.x < 2;
-  const int k_stages_full = kt / 4;             // k-stages with all four atoms
+  const int k_stages_full = kt / kAtomsPerStage;   // k-stages with all their atoms
 
   if (warp == kWarpLoadA || warp == kWarpLoadB) {
     // ============================ operand loaders ============================
@@ -353,8 +398,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     {
       const bool is_a = warp == kWarpLoadA;
       const CUtensorMap* tmap = is_a ? &tmap_a : &tmap_b;
-      const uint32_t bytes = is_a ? Cfg::kABytes : Cfg::kBBytes;
-      const uint32_t dst0 = stage_u32 + (is_a ? 0 : Cfg::kABytes);
+      const uint32_t bytes = is_a ? a_bytes : Cfg::kBBytes;
+      const uint32_t dst0 = stage_u32 + (is_a ? 0 : kSub * a_bytes);
       const bool no_loads = (p.debug & 2) != 0;   // experiment: barriers only
       int stage = 0, iter = 0;
       uint32_t phase = 0, dst = dst0, full_a = full_u32, full_t = full_target_u32, empty_a = empty_u32;
@@ -365,8 +410,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                              : t.g * p.b_group_rows + t.nt * BN + static_cast<int>(cta_rank) * Cfg::kBRows;
         const int ks_begin = (k_stages * t.split) / p.num_splits;
         const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
-        int c0 = ks_begin * kStageKBytes;
-        for (int ks = ks_begin; ks < ks_end; ++ks, c0 += kStageKBytes) {
+        int c0 = ks_begin * kSub * kStageKBytes;
+        for (int ks = ks_begin; ks < ks_end; ++ks, c0 += kSub * kStageKBytes) {
           if (tracing && lane == 0) trace_stamp(p, is_a ? 0 : 4, iter, 0);
           if (!ptx::mbar_wait(empty_a, phase ^ 1, abort_flag, 1)) { ok = false; break; }
           if (tracing && lane == 0) trace_stamp(p, is_a ? 0 : 4, iter, 1);
@@ -375,14 +420,19 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (no_loads) {
               if (leader) ptx::mbar_arrive(full_a);
             } else if constexpr (kTwoCta) {
-              if (leader) ptx::mbar_arrive_expect_tx(full_a, 2 * bytes);
-              ptx::tma_load_2d_pair(dst, tmap, full_t, c0, row);
+              if (leader) ptx::mbar_arrive_expect_tx(full_a, 2 * kSub * bytes);
+#pragma unroll
+              for (int sub = 0; sub < kSub; ++sub)
+                ptx::tma_load_2d_pair(dst + sub * bytes, tmap, full_t, c0 + sub * kStageKBytes, row);
             } else {
-              ptx::mbar_arrive_expect_tx(full_a, bytes);
-              ptx::tma_load_2d(dst, tmap, full_a, c0, row);
+              // a sub-stage that starts behind the end of K is filled with zeros by the load
+              ptx::mbar_arrive_expect_tx(full_a, kSub * bytes);
+#pragma unroll
+              for (int sub = 0; sub < kSub; ++sub)
+                ptx::tma_load_2d(dst + sub * bytes, tmap, full_a, c0 + sub * kStageKBytes, row);
             }
           }
-          dst += Cfg::kStageBytes; full_a += 8; full_t += 8; empty_a += 8;
+          dst += stage_bytes; full_a += 8; full_t += 8; empty_a += 8;
           if (++stage == kStages) {
             stage = 0; phase ^= 1; dst = dst0; full_a = full_u32; full_t = full_target_u32; empty_a = empty_u32;
           }
@@ -412,23 +462,26 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         int sfa_row = t.mt * kCtas + static_cast<int>(cta_rank);
         if (sfa_row >= p.sfa_atom_rows) sfa_row = p.sfa_atom_rows - 1;
         const uint8_t* sfa_src = p.sfa + t.g * p.sfa_group_stride +
-                                 (static_cast<long long>(sfa_row) * kt + ks_begin * 4) * kAtomBytes;
+                                 (static_cast<long long>(sfa_row) * kt + ks_begin * kAtomsPerStage) * kAtomBytes;
         const uint8_t* sfb_src = p.sfb + t.g * p.sfb_group_stride +
-                                 (static_cast<long long>(sf_tile0) * kt + ks_begin * 4) * kAtomBytes;
+                                 (static_cast<long long>(sf_tile0) * kt + ks_begin * kAtomsPerStage) * kAtomBytes;
         const long long sfb_group_step = static_cast<long long>(kt) * kAtomBytes;
-        for (int ks = ks_begin; ks < ks_end; ++ks, sfa_src += 4 * kAtomBytes, sfb_src += 4 * kAtomBytes) {
+        for (int ks = ks_begin; ks < ks_end;
+             ++ks, sfa_src += kAtomsPerStage * kAtomBytes, sfb_src += kAtomsPerStage * kAtomBytes) {
           if (!ptx::mbar_wait(free_a, phase ^ 1, abort_flag, 8)) { ok = false; break; }
           if (tracing && lane == 0) trace_stamp(p, 2, iter, 0);
-          const uint32_t sf_bytes = ks < k_stages_full ? 4u * kAtomBytes : static_cast<uint32_t>(kt - ks * 4) * kAtomBytes;
+          const uint32_t sf_bytes = ks < k_stages_full ? static_cast<uint32_t>(kAtomsPerStage) * kAtomBytes
+                                                       : static_cast<uint32_t>(kt - ks * kAtomsPerStage) * kAtomBytes;
           if (ptx::elect_one()) {
             if (no_loads) {
               ptx::mbar_arrive(landed_a);
             } else {
               ptx::mbar_arrive_expect_tx(landed_a, sf_bytes * (1 + sfb_groups));
               ptx::bulk_load(dst, sfa_src, sf_bytes, landed_a);
-              ptx::bulk_load(dst + Cfg::kSfaBytes, sfb_src, sf_bytes, landed_a);
+              ptx::bulk_load(dst + kSub * Cfg::kSfaBytes, sfb_src, sf_bytes, landed_a);
               if (Cfg::kSfbGroups == 2 && sfb_groups == 2)
-                ptx::bulk_load(dst + Cfg::kSfaBytes + 4 * kAtomBytes, sfb_src + sfb_group_step, sf_bytes, landed_a);
+                ptx::bulk_load(dst + kSub * Cfg::kSfaBytes + kAtomsPerStage * kAtomBytes, sfb_src + sfb_group_step,
+                               sf_bytes, landed_a);
             }
           }
           if (tracing && lane == 0) trace_stamp(p, 2, iter, 1);
@@ -444,7 +497,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (leader) {
       constexpr uint32_t idesc = ptx::make_idesc_nvfp4(kTileM, BN);
       constexpr uint16_t kAllCtas = kTwoCta ? 3 : 1;
-      constexpr uint32_t kDescStep = Cfg::kStageBytes >> 4;        // descriptor units per stage
+      const uint32_t kDescStep = stage_bytes >> 4;                 // descriptor units per stage
+      const uint32_t a_desc_sub = a_bytes >> 4;                    // ... per sub-stage of A
       const uint32_t a_lo0 = ptx::kmajor_sw128_desc_lo(stage_u32);
       const uint32_t sf_col0 = tmem_base + Cfg::kSfBase;
       const bool no_mma = (p.debug & 1) != 0;   // experiment: data path only
@@ -474,36 +528,37 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (!ready && !ptx::mbar_wait(full_a, phase, abort_flag, 3)) { ok = false; break; }
           if (tracing && lane == 0) trace_stamp(p, 1, iter, 1);
           ptx::tc_fence_after_sync();
-          const uint32_t b_lo = a_lo + (Cfg::kABytes >> 4);
+          const uint32_t b_lo = a_lo + kSub * a_desc_sub;
           const uint32_t sfb_col = sf_col + 16 + sfb_sub;
           const bool full_stage = ks < k_stages_full;
           const bool last_ring = stage + 1 == kStages;
           const uint32_t next_full = last_ring ? full_u32 : full_a + 8;
           const uint32_t next_phase = last_ring ? phase ^ 1 : phase;
-          // 64 E2M1 values = 32 bytes along K: +2 in the descriptor's 16-byte address field
+          // MMA number i of the stage (sub-stage i / 4, atom i % 4): 64 E2M1 values = 32 bytes along K
+          // are +2 in the descriptor's 16-byte address field; a sub-stage is one operand block further
+          auto issue = [&](int i, uint32_t accumulate) {
+            const int sub = i >> 2, j = i & 3;
+            ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_lo + sub * a_desc_sub + 2 * j,
+                                     b_lo + sub * (Cfg::kBBytes >> 4) + 2 * j, ptx::kKmajorSw128DescHi, idesc,
+                                     sf_col + sub * Cfg::kSfColsPerSub + 4 * j,
+                                     sfb_col + sub * Cfg::kSfColsPerSub + j * Cfg::kSfbColsPerMma, accumulate);
+          };
           if (full_stage && !no_mma) {
             if (ptx::elect_one()) {
-              ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_lo, b_lo, ptx::kKmajorSw128DescHi, idesc, sf_col, sfb_col,
-                                       ks > ks_begin ? 1u : 0u);
-              ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_lo + 2, b_lo + 2, ptx::kKmajorSw128DescHi, idesc, sf_col + 4,
-                                       sfb_col + Cfg::kSfbColsPerMma, 1u);
-              ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_lo + 4, b_lo + 4, ptx::kKmajorSw128DescHi, idesc, sf_col + 8,
-                                       sfb_col + 2 * Cfg::kSfbColsPerMma, 1u);
+              issue(0, ks > ks_begin ? 1u : 0u);
+#pragma unroll
+              for (int i = 1; i < kAtomsPerStage - 1; ++i) issue(i, 1u);
             }
             ready = ks + 1 < ks_end && __all_sync(0xffffffffu, ptx::mbar_test_wait(next_full, next_phase));
             if (ptx::elect_one()) {
-              ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_lo + 6, b_lo + 6, ptx::kKmajorSw128DescHi, idesc, sf_col + 12,
-                                       sfb_col + 3 * Cfg::kSfbColsPerMma, 1u);
+              issue(kAtomsPerStage - 1, 1u);
               ptx::tc_commit<kCtas>(empty_a, kAllCtas);
             }
           } else {
             ready = false;
             if (ptx::elect_one()) {
-              const int atoms = no_mma ? 0 : kt - ks * 4;
-              for (int j = 0; j < atoms && j < 4; ++j)
-                ptx::tc_mma_nvfp4<kCtas>(tmem_acc, a_lo + 2 * j, b_lo + 2 * j, ptx::kKmajorSw128DescHi, idesc,
-                                         sf_col + 4 * j, sfb_col + j * Cfg::kSfbColsPerMma,
-                                         (j > 0 || ks > ks_begin) ? 1u : 0u);
+              const int atoms = no_mma ? 0 : kt - ks * kAtomsPerStage;
+              for (int i = 0; i < atoms && i < kAtomsPerStage; ++i) issue(i, (i > 0 || ks > ks_begin) ? 1u : 0u);
               ptx::tc_commit<kCtas>(empty_a, kAllCtas);
             }
           }
@@ -557,36 +612,43 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           // 1. atoms of this k-stage: shared memory -> registers. Every lane polls: a
           //    single-lane wait costs a vote and a broadcast per call.
           if (tracing && q == 0 && lane == 0) trace_stamp(p, 3, iter, 0);
-          const int atoms = ks < k_stages_full ? 4 : kt - ks * 4;
-          uint32_t ra[16];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (j < atoms) v = ptx::ld_shared_v4(src + j * kAtomBytes);
-            ra[4 * j] = v.x; ra[4 * j + 1] = v.y; ra[4 * j + 2] = v.z; ra[4 * j + 3] = v.w;
-          }
-          uint32_t rb[4 * Cfg::kSfbColsPerMma];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-#pragma unroll
-            for (int gi = 0; gi < Cfg::kSfbGroups; ++gi) {
-              uint4 v = make_uint4(0u, 0u, 0u, 0u);
-              if (j < atoms) v = ptx::ld_shared_v4(src + Cfg::kSfaBytes + (gi * 4 + j) * kAtomBytes);
-              const int c = j * Cfg::kSfbColsPerMma + 4 * gi;
-              rb[c] = v.x; rb[c + 1] = v.y; rb[c + 2] = v.z; rb[c + 3] = v.w;
-            }
-          }
-          // 2. registers -> this k-stage's tensor-memory buffer, once the MMAs of the k-stage
-          //    that used the buffer last (sf_depth k-stages ago) are done: their commit
-          //    completes a phase of that k-stage's `empty` barrier
+          const int atoms = ks < k_stages_full ? kAtomsPerStage : kt - ks * kAtomsPerStage;
+          // the tensor-memory buffer is free once the MMAs of the k-stage that used it last
+          // (sf_depth k-stages ago) are done: their commit completes a phase of that k-stage's
+          // `empty` barrier
           if (need_lag && !ptx::mbar_wait(lag_a, lag_phase, abort_flag, 6)) { ok = false; break; }
           ptx::tc_fence_after_sync();
-          if (!no_store) {
-            ptx::tmem_st_32x32b_x16(taddr, ra);
-            if constexpr (Cfg::kSfbGroups == 2) ptx::tmem_st_32x32b_x32(taddr + 16, rb);
-            else ptx::tmem_st_32x32b_x16(taddr + 16, rb);
-            ptx::tmem_st_wait();
+#pragma unroll
+          for (int sub = 0; sub < kSub; ++sub) {
+            // 1. atoms of this sub-stage: shared memory -> registers
+            const int sub_atoms = atoms - 4 * sub;
+            uint32_t ra[16];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 v = make_uint4(0u, 0u, 0u, 0u);
+              if (j < sub_atoms) v = ptx::ld_shared_v4(src + (sub * 4 + j) * kAtomBytes);
+              ra[4 * j] = v.x; ra[4 * j + 1] = v.y; ra[4 * j + 2] = v.z; ra[4 * j + 3] = v.w;
+            }
+            uint32_t rb[4 * Cfg::kSfbColsPerMma];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+#pragma unroll
+              for (int gi = 0; gi < Cfg::kSfbGroups; ++gi) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (j < sub_atoms)
+                  v = ptx::ld_shared_v4(src + kSub * Cfg::kSfaBytes + (gi * kAtomsPerStage + sub * 4 + j) * kAtomBytes);
+                const int c = j * Cfg::kSfbColsPerMma + 4 * gi;
+                rb[c] = v.x; rb[c + 1] = v.y; rb[c + 2] = v.z; rb[c + 3] = v.w;
+              }
+            }
+            // 2. registers -> the sub-stage's part of this k-stage's tensor-memory buffer
+            if (!no_store) {
+              ptx::tmem_st_32x32b_x16(taddr + sub * Cfg::kSfColsPerSub, ra);
+              if constexpr (Cfg::kSfbGroups == 2) ptx::tmem_st_32x32b_x32(taddr + sub * Cfg::kSfColsPerSub + 16, rb);
+              else ptx::tmem_st_32x32b_x16(taddr + sub * Cfg::kSfColsPerSub + 16, rb);
+            }
           }
+          if (!no_store) ptx::tmem_st_wait();
           ptx::tc_fence_before_sync();
           __syncwarp();
           if (ptx::elect_one()) {
