@@ -226,6 +226,21 @@ B200_NVFP4_API int b200_nvfp4_expert_moe(void* output, const void* input, const 
                                          int num_expert_local, int grouped_scale_m_pad,
                                          b200_stream_t stream);
 
+/* Gate/up grouped GEMM with SiLU(gate) * up and the NVFP4 quantisation fused into its epilogue
+ * (no counterpart in the reference, which runs group_gemm_nvfp4_async and
+ * act_mul_and_quant_nvfp4_async one after the other, src/fused_moe/fused_moe.cu:52-63; the fused
+ * MoE entry points of this library use this kernel when B200_NVFP4_FUSED_GATE_UP=1 is set in the
+ * environment - on the measured shapes the two separate kernels are faster). w is [G, 2I, K/2] with the gate rows first;
+ * output is packed E2M1 [m, I/2], output_scale one region of output_scale_m_pad rows per group -
+ * the bytes the two separate calls produce. intermediate_size must be a multiple of 128
+ * (otherwise B200_NVFP4_CUTLASS_NOT_SUPPORTED is returned and nothing is launched). tiles /
+ * cu_tiles as in b200_nvfp4_grouped_gemm (may be null). */
+B200_NVFP4_API int b200_nvfp4_grouped_gemm_swiglu_quant(
+    void* output, void* output_scale, const void* x, const void* w, const void* seqlens,
+    const void* cu_seqlens, const void* x_scale, const void* w_scale, void* tiles, void* cu_tiles,
+    int num_group, int m, int intermediate_size, int k, int m_scale_pad, int output_scale_m_pad,
+    int num_seq_per_group_avg, b200_stream_t stream);
+
 /* Router step in front of the routed layer (no counterpart in the reference library, whose
  * entry points take topk_ids / topk_weights as inputs): logits FP32 [T, E] -> sigmoid scores,
  * the num_topk largest per token (ties to the lower expert id) as int32 ids [T, k], and FP32

@@ -43,6 +43,7 @@ _SIGNATURES = {
     "b200_nvfp4_fused_moe": (ci, [vp] * 23 + [ci] * 9 + [vp]),
     "b200_nvfp4_expert_moe_workspace_bytes": (C.c_size_t, [ci] * 5),
     "b200_nvfp4_moe_router_topk": (ci, [vp, vp, vp, ci, ci, ci, vp]),
+    "b200_nvfp4_grouped_gemm_swiglu_quant": (ci, [vp] * 10 + [ci] * 7 + [vp]),
     "b200_nvfp4_ep_record_bytes": (C.c_size_t, [ci, ci]),
     "b200_nvfp4_ep_dest_ranks": (ci, [vp, vp, ci, ci, ci, ci, vp]),
     "b200_nvfp4_ep_pack_rows": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),

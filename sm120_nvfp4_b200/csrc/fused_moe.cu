@@ -7,12 +7,41 @@
 // host synchronisation, no allocation.
 #include <cstdint>
 
+#include <cstdlib>
+
 #include "host_common.hpp"
 #include "internal.hpp"
 
 namespace b200 {
 
 namespace {
+
+// Gate/up GEMM -> down-projection input: the two separate steps of the reference by default. With
+// B200_NVFP4_FUSED_GATE_UP=1 in the environment the SiLU * up and the quantisation run in the GEMM's
+// epilogue instead (one kernel, the FP16 product never reaches memory, gate_up_output stays
+// untouched; same bits). Measured on the DeepSeek-shaped layer the fused form is slower (1.98 ms
+// against 1.71 ms per layer): the exact expf and the two IEEE divisions per value cost ~50
+// instructions, which 8 epilogue warps per SM cannot hide behind the mainloop the way a
+// full-occupancy streaming kernel can.
+int gate_up_stage(void* down_input, void* down_input_scale, void* gate_up_output, const void* x,
+                  const void* w, const void* seqlens, const void* cu_seqlens, const void* x_scale,
+                  const void* w_scale, void* tiles, void* cu_tiles, int num_expert_local, int total_rows,
+                  int intermediate_size, int hidden_size, int m_pad, int avg, cudaStream_t stream) {
+  static const bool fused = [] { const char* e = std::getenv("B200_NVFP4_FUSED_GATE_UP"); return e && e[0] == '1'; }();
+  if (fused) {
+    const int st = gemm_grouped_swiglu(down_input, down_input_scale, x, w, seqlens, cu_seqlens, x_scale, w_scale,
+                                       tiles, cu_tiles, num_expert_local, total_rows, intermediate_size,
+                                       hidden_size, m_pad, m_pad, avg, stream);
+    if (st != B200_NVFP4_CUTLASS_NOT_SUPPORTED) return st;
+  }
+  int st = gemm_grouped(gate_up_output, x, w, seqlens, cu_seqlens, x_scale, w_scale, tiles, cu_tiles,
+                        num_expert_local, total_rows, intermediate_size * 2, hidden_size, m_pad, avg, nullptr,
+                        stream);
+  if (st != B200_NVFP4_SUCCESS) return st;
+  return moe_act_mul_and_quant(down_input, down_input_scale, gate_up_output, seqlens, cu_seqlens,
+                               num_expert_local, total_rows, m_pad, intermediate_size,
+                               /*zero_scales=*/false, stream);
+}
 
 constexpr size_t kWorkspaceAlignment = 256;
 
@@ -67,14 +96,9 @@ int fused_moe(void* output, const void* input, const void* input_scale, void* ga
                                 num_expert_local, rank_ep, input_scale_m_pad, grouped_scale_m_pad,
                                 /*zero_scales=*/false, stream);
   if (st != B200_NVFP4_SUCCESS) return st;
-  st = gemm_grouped(gate_up_output, gate_up_input, gate_up_weight, seqlens, cu_seqlens,
-                    gate_up_input_scale, gate_up_weight_scale, tiles, cu_tiles, num_expert_local,
-                    total, intermediate_size * 2, hidden_size, grouped_scale_m_pad, avg, nullptr,
-                    stream);
-  if (st != B200_NVFP4_SUCCESS) return st;
-  st = moe_act_mul_and_quant(down_input, down_input_scale, gate_up_output, seqlens, cu_seqlens,
-                             num_expert_local, total, grouped_scale_m_pad, intermediate_size,
-                             /*zero_scales=*/false, stream);
+  st = gate_up_stage(down_input, down_input_scale, gate_up_output, gate_up_input, gate_up_weight, seqlens,
+                     cu_seqlens, gate_up_input_scale, gate_up_weight_scale, tiles, cu_tiles, num_expert_local,
+                     total, intermediate_size, hidden_size, grouped_scale_m_pad, avg, stream);
   if (st != B200_NVFP4_SUCCESS) return st;
   st = gemm_grouped(down_output, down_input, down_weight, seqlens, cu_seqlens, down_input_scale,
                     down_weight_scale, tiles, cu_tiles, num_expert_local, total, hidden_size,
@@ -103,13 +127,9 @@ int expert_moe(void* output, const void* input, const void* input_scale, const v
   void* tiles = base + c.tiles;
   void* cu_tiles = base + c.cu_tiles;
   const int avg = total_rows / num_expert_local;
-  int st = gemm_grouped(gate_up_output, input, gate_up_weight, seqlens, cu_seqlens, input_scale,
-                        gate_up_weight_scale, tiles, cu_tiles, num_expert_local, total_rows,
-                        intermediate_size * 2, hidden_size, grouped_scale_m_pad, avg, nullptr, stream);
-  if (st != B200_NVFP4_SUCCESS) return st;
-  st = moe_act_mul_and_quant(down_input, down_input_scale, gate_up_output, seqlens, cu_seqlens,
-                             num_expert_local, total_rows, grouped_scale_m_pad, intermediate_size,
-                             /*zero_scales=*/false, stream);
+  int st = gate_up_stage(down_input, down_input_scale, gate_up_output, input, gate_up_weight, seqlens,
+                         cu_seqlens, input_scale, gate_up_weight_scale, tiles, cu_tiles, num_expert_local,
+                         total_rows, intermediate_size, hidden_size, grouped_scale_m_pad, avg, stream);
   if (st != B200_NVFP4_SUCCESS) return st;
   return gemm_grouped(output, down_input, down_weight, seqlens, cu_seqlens, down_input_scale,
                       down_weight_scale, tiles, cu_tiles, num_expert_local, total_rows, hidden_size,
@@ -214,6 +234,16 @@ int b200_nvfp4_fused_moe(void* output, const void* input, const void* input_scal
                          num_tokens, hidden_size, intermediate_size, num_topk, num_expert_total,
                          num_expert_local, rank_ep, input_scale_m_pad, grouped_scale_m_pad,
                          static_cast<cudaStream_t>(stream));
+}
+
+int b200_nvfp4_grouped_gemm_swiglu_quant(void* output, void* output_scale, const void* x, const void* w,
+                                         const void* seqlens, const void* cu_seqlens, const void* x_scale,
+                                         const void* w_scale, void* tiles, void* cu_tiles, int num_group, int m,
+                                         int intermediate_size, int k, int m_scale_pad, int output_scale_m_pad,
+                                         int num_seq_per_group_avg, b200_stream_t stream) {
+  return b200::gemm_grouped_swiglu(output, output_scale, x, w, seqlens, cu_seqlens, x_scale, w_scale, tiles,
+                                   cu_tiles, num_group, m, intermediate_size, k, m_scale_pad, output_scale_m_pad,
+                                   num_seq_per_group_avg, static_cast<cudaStream_t>(stream));
 }
 
 int b200_nvfp4_moe_router_topk(const void* logits, void* topk_ids, void* topk_weights,

@@ -63,12 +63,16 @@ struct LaunchSpec {
   int expected_m_tiles;    // estimate used to pick the tile width and the grid
   bool exact_m_tiles;      // expected_m_tiles is exact (dense) rather than a hint (grouped)
   int avg_group_rows;      // rows per group (exact for dense, a hint for grouped)
+  int swiglu_inter = 0;    // fused gate/up: intermediate size I (n == 2 * I), else 0
+  void* q_out = nullptr;
+  void* q_scale = nullptr;
+  long long q_scale_group_stride = 0;
 };
 
-template <int BN, bool F32, bool kTwoCta>
+template <int BN, bool F32, bool kTwoCta, bool kSwiGlu = false>
 int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t stream) {
   using Cfg = GemmCfg<BN, kTwoCta>;
-  auto kernel = nvfp4_gemm_kernel<BN, F32, kTwoCta>;
+  auto kernel = nvfp4_gemm_kernel<BN, F32, kTwoCta, kSwiGlu>;
   static std::once_flag once[64];
   static cudaError_t attr_status[64];
   std::call_once(once[dev.device], [&] {
@@ -89,7 +93,7 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   if (!encode_tmap_2d_u8(&tmap_a, s.a, static_cast<uint64_t>(s.a_rows_total), row_bytes, a_box_rows,
                          kStageKBytes, CU_TENSOR_MAP_SWIZZLE_128B) ||
       !encode_tmap_2d_u8(&tmap_b, s.b, static_cast<uint64_t>(s.b_rows_total), row_bytes,
-                         Cfg::kBRows, kStageKBytes, CU_TENSOR_MAP_SWIZZLE_128B)) {
+                         kSwiGlu ? 128 : Cfg::kBRows, kStageKBytes, CU_TENSOR_MAP_SWIZZLE_128B)) {
     return B200_NVFP4_CUDA_ERROR;
   }
 
@@ -99,7 +103,7 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   CUtensorMap tmap_out = tmap_a;
   const int box_cols = F32 ? 32 : 64;
   const long long out_rows = static_cast<long long>(s.a_rows_total) * (s.num_splits > 1 ? s.num_splits : 1);
-  const bool tma_store = BN >= 128 && s.n >= box_cols && out_rows < 0x7fffffffLL &&
+  const bool tma_store = !kSwiGlu && BN >= 128 && s.n >= box_cols && out_rows < 0x7fffffffLL &&
                          encode_tmap_2d_out(&tmap_out, s.out, static_cast<uint64_t>(out_rows),
                                             static_cast<uint64_t>(s.n), F32, 32, box_cols);
 
@@ -126,6 +130,10 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   p.tiles_out = s.tiles_out;
   p.cu_tiles_out = s.cu_tiles_out;
   p.error = device_error_word();
+  p.swiglu_inter = s.swiglu_inter;
+  p.q_out = static_cast<uint8_t*>(s.q_out);
+  p.q_scale = static_cast<uint8_t*>(s.q_scale);
+  p.q_scale_group_stride = s.q_scale_group_stride;
   p.a_sub_bytes = a_sub_bytes;
   p.num_stages = Cfg::stages_for(s.num_groups, a_sub_bytes);
   p.num_sf_slots = Cfg::sf_slots_for(s.num_groups, a_sub_bytes);
@@ -135,7 +143,7 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   if (p.debug & 64) { void* tp = nullptr; if (cudaGetSymbolAddress(&tp, g_trace) == cudaSuccess) p.trace = static_cast<unsigned long long*>(tp); }
 
   // One persistent worker (a CTA, or a pair of CTAs) per SM (or per SM pair).
-  const int n_tiles = (s.n + BN - 1) / BN;
+  const int n_tiles = kSwiGlu ? s.swiglu_inter / 128 : (s.n + BN - 1) / BN;
   const long long m_tiles = kTwoCta ? (s.expected_m_tiles + 1) / 2 : s.expected_m_tiles;
   long long tasks = m_tiles * n_tiles * s.num_splits;
   int workers = dev.sm_count / Cfg::kCtas;
@@ -388,6 +396,70 @@ int gemm_grouped(void* y, const void* x, const void* w, const void* seqlens,
   s.exact_m_tiles = false;
   s.avg_group_rows = avg;
   return launch_gemm(s, stream, env_tile_n());
+}
+
+// Gate/up grouped GEMM with the SiLU * up + NVFP4 quantisation in its epilogue: w is
+// [G, 2I, K/2] (gate rows, then up rows), the result is what moe_act_mul_and_quant would
+// make of the FP16 product - packed [m, I/2] and per-group scale regions of q_scale_m_pad rows -
+// bit for bit. Returns B200_NVFP4_CUTLASS_NOT_SUPPORTED for shapes the fused tile does not
+// cover (I not a multiple of 128); the caller then runs the two separate steps.
+int gemm_grouped_swiglu(void* q_out, void* q_scale, const void* x, const void* w, const void* seqlens,
+                        const void* cu_seqlens, const void* x_scale, const void* w_scale, void* tiles,
+                        void* cu_tiles, int num_group, int m, int inter, int k, int m_scale_pad,
+                        int q_scale_m_pad, int num_seq_per_group_avg, cudaStream_t stream) {
+  if (inter <= 0 || (inter % 128) != 0) return B200_NVFP4_CUTLASS_NOT_SUPPORTED;
+  const int n = 2 * inter;
+  if (num_group <= 0 || num_group > kMaxGroups || !valid_shape(m, n, k) || q_out == nullptr ||
+      q_scale == nullptr || x == nullptr || w == nullptr || seqlens == nullptr ||
+      cu_seqlens == nullptr || x_scale == nullptr || w_scale == nullptr || m_scale_pad < 128 ||
+      (m_scale_pad % 128) != 0 || q_scale_m_pad < 128 || (q_scale_m_pad % 128) != 0 ||
+      !aligned16(q_out) || !aligned16(q_scale) || !aligned16(x) || !aligned16(w) ||
+      !aligned16(x_scale) || !aligned16(w_scale)) {
+    return B200_NVFP4_INVALID_ARGUMENT;
+  }
+  const DeviceInfo& dev = current_device_info();
+  if (!dev.ok) return B200_NVFP4_CUDA_ERROR;
+  if (!device_supported(dev)) return B200_NVFP4_UNSUPPORTED_DEVICE;
+  const int skp = scale_k_padded(k);
+  LaunchSpec s{};
+  s.num_groups = num_group;
+  s.m_uniform = 0;
+  s.a_rows_total = m;
+  s.n = n;
+  s.k = k;
+  s.a = x;
+  s.b = w;
+  s.sfa = x_scale;
+  s.sfb = w_scale;
+  s.sfa_group_stride = static_cast<long long>(m_scale_pad) * skp;
+  s.sfb_group_stride = static_cast<long long>(align_up_int(n, 128)) * skp;
+  s.b_group_rows = n;
+  s.b_rows_total = num_group * n;
+  s.seqlens = static_cast<const int*>(seqlens);
+  s.cu_seqlens = static_cast<const int*>(cu_seqlens);
+  s.out = q_out;   // not written as a matrix; kept non-null for the common checks
+  s.out_f32 = false;
+  s.num_splits = 1;
+  s.tiles_out = static_cast<int*>(tiles);
+  s.cu_tiles_out = static_cast<int*>(cu_tiles);
+  int avg = num_seq_per_group_avg > 0 ? num_seq_per_group_avg : (m + num_group - 1) / num_group;
+  long long est = static_cast<long long>(num_group) * ((avg + kBlockM - 1) / kBlockM);
+  const long long upper = static_cast<long long>(m) / kBlockM + num_group;
+  if (est > upper) est = upper;
+  if (est < 1) est = 1;
+  s.expected_m_tiles = static_cast<int>(est);
+  s.exact_m_tiles = false;
+  s.avg_group_rows = avg;
+  s.swiglu_inter = inter;
+  s.q_out = q_out;
+  s.q_scale = q_scale;
+  s.q_scale_group_stride = static_cast<long long>(q_scale_m_pad) * scale_k_padded(inter);
+  // tall groups on CTA pairs, short ones on single CTAs: the rule of the plain grouped GEMM
+  const int forced = env_tile_n();
+  const bool pair = forced ? forced == 512
+                           : (avg >= 384 && ((est + 1) / 2) * (inter / 128) >= dev.sm_count / 2);
+  return pair ? launch_instance<256, false, true, true>(s, dev, stream)
+              : launch_instance<256, false, false, true>(s, dev, stream);
 }
 
 }  // namespace b200

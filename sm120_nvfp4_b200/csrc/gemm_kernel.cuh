@@ -41,6 +41,7 @@
 
 #include <cuda_fp16.h>
 
+#include "nvfp4_math.cuh"
 #include "ptx.cuh"
 
 namespace b200 {
@@ -93,6 +94,13 @@ struct GemmParams {
   int num_sf_slots;           // depth of the scale-atom ring in shared memory (<= kMaxSfSlots)
   int tma_store;              // 1: the output tensor map is valid, full 32-row slabs go out by TMA store
   int out_rows_per_split;     // rows between split-K slices in the output tensor map (M), 0 without split
+  // Fused gate/up variant (kSwiGlu kernels): B holds [gate rows 0..I) ; up rows I..2I) per group, a
+  // tile computes 128 gate and the matching 128 up columns, and the epilogue writes
+  // NVFP4(silu(gate) * up) instead of the FP16 product.
+  int swiglu_inter;           // I (multiple of 128), 0 for plain GEMMs
+  uint8_t* q_out;             // packed E2M1 [rows, I/2]
+  uint8_t* q_scale;           // UE4M3 scale regions, one per group, indexed by the row inside the group
+  long long q_scale_group_stride;
   int debug;                  // bit 64: record time stamps into `trace` (0 in production)
   unsigned long long* trace;  // optional time-stamp buffer (debug bit 64), else nullptr
 };
@@ -211,12 +219,13 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <int BN, bool kOutF32, bool kTwoCta>
+template <int BN, bool kOutF32, bool kTwoCta, bool kSwiGlu = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
   using Cfg = GemmCfg<BN, kTwoCta>;
+  static_assert(!kSwiGlu || (BN == 256 && !kOutF32), "the fused gate/up epilogue is built on 256-column FP16 tiles");
   if ((p.debug & 64) && p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
     unsigned long long ns;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
@@ -370,7 +379,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
   const uint32_t tmem_base = *tmem_holder;
   const int total_mt = s_cu_tiles[G];
-  const int n_tiles = (p.n + BN - 1) / BN;
+  // fused gate/up: a tile covers 128 columns of the intermediate (its gate and its up half)
+  const int n_tiles = kSwiGlu ? p.swiglu_inter / 128 : (p.n + BN - 1) / BN;
   const int total_tasks = total_mt * n_tiles * p.num_splits;
   const int kt = (p.k + 63) / 64;               // scale atoms along K
   constexpr int kSub = Cfg::kSub;
@@ -406,8 +416,10 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       for (int task = worker; task < total_tasks && ok; task += num_workers) {
         TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
-        const int row = is_a ? s_row0[t.g] + t.mt * kTileM + static_cast<int>(cta_rank) * kBlockM
-                             : t.g * p.b_group_rows + t.nt * BN + static_cast<int>(cta_rank) * Cfg::kBRows;
+        int row;
+        if (is_a) row = s_row0[t.g] + t.mt * kTileM + static_cast<int>(cta_rank) * kBlockM;
+        else if constexpr (kSwiGlu) row = t.g * p.b_group_rows + t.nt * 128 + (kTwoCta ? static_cast<int>(cta_rank) * p.swiglu_inter : 0);
+        else row = t.g * p.b_group_rows + t.nt * BN + static_cast<int>(cta_rank) * Cfg::kBRows;
         const int ks_begin = (k_stages * t.split) / p.num_splits;
         const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
         int c0 = ks_begin * kSub * kStageKBytes;
@@ -427,9 +439,14 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             } else {
               // a sub-stage that starts behind the end of K is filled with zeros by the load
               ptx::mbar_arrive_expect_tx(full_a, kSub * bytes);
+              if (kSwiGlu && !is_a) {   // 128 gate rows, then the 128 up rows I further down (128-row box)
+                ptx::tma_load_2d(dst, tmap, full_a, c0, row);
+                ptx::tma_load_2d(dst + bytes / 2, tmap, full_a, c0, row + p.swiglu_inter);
+              } else {
 #pragma unroll
-              for (int sub = 0; sub < kSub; ++sub)
-                ptx::tma_load_2d(dst + sub * bytes, tmap, full_a, c0 + sub * kStageKBytes, row);
+                for (int sub = 0; sub < kSub; ++sub)
+                  ptx::tma_load_2d(dst + sub * bytes, tmap, full_a, c0 + sub * kStageKBytes, row);
+              }
             }
           }
           dst += stage_bytes; full_a += 8; full_t += 8; empty_a += 8;
@@ -451,9 +468,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       for (int task = worker; task < total_tasks && ok; task += num_workers) {
         TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
-        const int sf_tile0 = (t.nt * BN) / 128;
+        const int sf_tile0 = kSwiGlu ? t.nt : (t.nt * BN) / 128;
         int sfb_groups = Cfg::kSfbGroups;
-        if (sf_tile0 + sfb_groups > n_sf_tiles) sfb_groups = n_sf_tiles - sf_tile0;
+        if (!kSwiGlu && sf_tile0 + sfb_groups > n_sf_tiles) sfb_groups = n_sf_tiles - sf_tile0;
         const int ks_begin = (k_stages * t.split) / p.num_splits;
         const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
         // A slab that lies wholly behind the group's scale region (second CTA of a pair on a short
@@ -465,7 +482,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                  (static_cast<long long>(sfa_row) * kt + ks_begin * kAtomsPerStage) * kAtomBytes;
         const uint8_t* sfb_src = p.sfb + t.g * p.sfb_group_stride +
                                  (static_cast<long long>(sf_tile0) * kt + ks_begin * kAtomsPerStage) * kAtomBytes;
-        const long long sfb_group_step = static_cast<long long>(kt) * kAtomBytes;
+        // second 128-row scale tile of the B tile: the next one, or the up half's (I / 128 tiles on)
+        const long long sfb_group_step = static_cast<long long>(kSwiGlu ? p.swiglu_inter / 128 : 1) * kt * kAtomBytes;
         for (int ks = ks_begin; ks < ks_end;
              ++ks, sfa_src += kAtomsPerStage * kAtomBytes, sfb_src += kAtomsPerStage * kAtomBytes) {
           if (!ptx::mbar_wait(free_a, phase ^ 1, abort_flag, 8)) { ok = false; break; }
@@ -747,7 +765,48 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       };
 
-      if constexpr (kOutF32) {
+      if constexpr (kSwiGlu) {
+        // Accumulator columns 0..127 are the gate, 128..255 the up projection of the same 128
+        // intermediate columns. This warp takes 64 of them (4 blocks of 16): both operands are
+        // rounded to FP16 first - the values the unfused path would have written and read back -
+        // then silu(gate) * up in FP32, quantised per 16 values with one UE4M3 scale.
+        const uint32_t g_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN + half * 64);
+        uint32_t payload[8];
+        uint32_t scale_word = 0;
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+          uint32_t gv[32], uv[32];
+          ptx::tmem_ld_32x32b_x32(g_addr + pass * 32, gv);
+          ptx::tmem_ld_32x32b_x32(g_addr + 128 + pass * 32, uv);
+          ptx::tmem_ld_wait();
+          if (pass == 1) release_accumulator();
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float gf = __half2float(__float2half_rn(__uint_as_float(gv[16 * b + i]) * alpha));
+              const float uf = __half2float(__float2half_rn(__uint_as_float(uv[16 * b + i]) * alpha));
+              v[i] = __fmul_rn(nvfp4_silu(gf), uf);
+            }
+            uint32_t lo, hi;
+            const uint8_t code = quantize_block16(v, lo, hi);
+            payload[(2 * pass + b) * 2] = lo;
+            payload[(2 * pass + b) * 2 + 1] = hi;
+            scale_word |= static_cast<uint32_t>(code) << (8 * (2 * pass + b));
+          }
+        }
+        if (row_ok) {
+          const int inter = p.swiglu_inter;
+          const int col = t.nt * 128 + half * 64;                 // first intermediate column of this lane's 64
+          uint4* dst = reinterpret_cast<uint4*>(p.q_out + out_row * (inter >> 1) + (col >> 1));
+          dst[0] = make_uint4(payload[0], payload[1], payload[2], payload[3]);
+          dst[1] = make_uint4(payload[4], payload[5], payload[6], payload[7]);
+          const int row_in_group = t.mt * kTileM + row_in_tile;
+          *reinterpret_cast<uint32_t*>(p.q_scale + t.g * p.q_scale_group_stride +
+                                       sf_offset(row_in_group, col >> 4, (inter + 63) >> 6)) = scale_word;
+        }
+      } else if constexpr (kOutF32) {
         float* dst = static_cast<float*>(p.out) + t.split * p.out_split_stride + out_row * p.n + col0;
 #pragma unroll 1
         for (int c = 0; c < kWarpCols / 32; ++c) {

@@ -24,6 +24,11 @@ int gemm_grouped(void* y, const void* x, const void* w, const void* seqlens,
                  void* cu_tiles, int num_group, int m, int n, int k, int m_scale_pad,
                  int num_seq_per_group_avg, const float* group_alpha, cudaStream_t stream);
 
+int gemm_grouped_swiglu(void* q_out, void* q_scale, const void* x, const void* w, const void* seqlens,
+                        const void* cu_seqlens, const void* x_scale, const void* w_scale, void* tiles,
+                        void* cu_tiles, int num_group, int m, int inter, int k, int m_scale_pad,
+                        int q_scale_m_pad, int num_seq_per_group_avg, cudaStream_t stream);
+
 int moe_count_and_gather(void* gate_up_input, void* gate_up_input_scale, const void* input,
                          const void* input_scale, const void* topk_ids, void* topk_pos,
                          void* seqlens, void* cu_seqlens, int num_tokens, int hidden_size,

@@ -292,3 +292,51 @@ def test_pack_weights_matches_row_quantiser(ops):
         kb = np.tile(np.arange(nkb, dtype=np.int32), n)
         off = oracle.sf_offsets(r, kb, k)
         np.testing.assert_array_equal(scales[e].cpu().numpy()[off], sc[off])
+
+
+@pytest.mark.parametrize("tile_n", [0, 512])
+@pytest.mark.parametrize("counts,hidden,inter", [([0, 1, 127, 129, 300], 256, 128), ([700, 5, 64], 512, 384)])
+def test_fused_gate_up_epilogue_matches_separate_steps(ops, counts, hidden, inter, tile_n):
+    # grouped GEMM + SiLU * up + quantisation in one kernel against the two separate kernels:
+    # packed payload and the scale bytes of live rows, bit for bit
+    from sm120_nvfp4_b200 import _lib
+    L = _lib.lib()
+    L.b200_nvfp4_set_tile_n(tile_n)
+    try:
+        counts = np.array(counts, np.int32)
+        groups, total = len(counts), int(counts.sum())
+        cu = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+        pad = max(128, (int(counts.max()) + 127) // 128 * 128)
+        g = torch.Generator(device="cuda").manual_seed(hidden + inter)
+        x = torch.randint(0, 256, (total, hidden // 2), dtype=torch.uint8, device="cuda", generator=g)
+        xs = torch.randint(0x30, 0x3c, (groups, pad * ops.scale_k_padded(hidden)), dtype=torch.uint8, device="cuda", generator=g)
+        w = torch.randint(0, 256, (groups, 2 * inter, hidden // 2), dtype=torch.uint8, device="cuda", generator=g)
+        ws = torch.randint(0x28, 0x34, (groups, 2 * inter * ops.scale_k_padded(hidden)), dtype=torch.uint8, device="cuda", generator=g)
+        dc, dcu = _dev(counts), _dev(cu)
+        st = _stream()
+        # separate steps
+        y = ops.grouped_gemm(x, w, dc, dcu, xs, ws)
+        want = torch.zeros((total, inter // 2), dtype=torch.uint8, device="cuda")
+        want_s = torch.zeros((groups, pad * ops.scale_k_padded(inter)), dtype=torch.uint8, device="cuda")
+        assert L.b200_nvfp4_moe_act_mul_and_quant(want.data_ptr(), want_s.data_ptr(), y.data_ptr(), dc.data_ptr(),
+                                                  dcu.data_ptr(), groups, total, pad, inter, 1, st) == 0
+        # fused
+        got = torch.zeros_like(want)
+        got_s = torch.zeros_like(want_s)
+        assert L.b200_nvfp4_grouped_gemm_swiglu_quant(got.data_ptr(), got_s.data_ptr(), x.data_ptr(), w.data_ptr(),
+                                                      dc.data_ptr(), dcu.data_ptr(), xs.data_ptr(), ws.data_ptr(),
+                                                      None, None, groups, total, inter, hidden, pad, pad, 0, st) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+        nkb = inter // 16
+        for e in range(groups):
+            n_rows = int(counts[e])
+            if n_rows == 0:
+                continue
+            r = np.repeat(np.arange(n_rows, dtype=np.int32), nkb)
+            kb = np.tile(np.arange(nkb, dtype=np.int32), n_rows)
+            off = oracle.sf_offsets(r, kb, inter)
+            np.testing.assert_array_equal(got_s[e].cpu().numpy()[off], want_s[e].cpu().numpy()[off])
+        assert int(want.sum()) > 0
+    finally:
+        L.b200_nvfp4_set_tile_n(0)
