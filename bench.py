@@ -323,7 +323,20 @@ class MoeWorkload:
         self.seq1 = torch.tensor([tokens], dtype=torch.int32, device=device)
         self.cu1 = torch.tensor([0, tokens], dtype=torch.int32, device=device)
         self.in_pad = (tokens + 127) // 128 * 128
-        self.layer = ExpertParallelMoE(self.gw, self.gws, self.dw, self.dws, experts) if world > 1 else None
+        # transport of the expert-parallel exchange: "p2p" = this library's kernels store into the
+        # peers' buffers over NVLink, "nccl" = all_to_all_single
+        self.transport = os.environ.get("B200_NVFP4_EP_TRANSPORT", "p2p") if world > 1 else "none"
+        self.layer = None
+        if world > 1:
+            try:
+                self.layer = ExpertParallelMoE(self.gw, self.gws, self.dw, self.dws, experts, transport=self.transport,
+                                               max_tokens=tokens, num_topk=topk)
+            except Exception as exc:   # no symmetric memory on this box: the all-to-all transport
+                if self.transport != "p2p":
+                    raise
+                print(f"[bench] p2p transport unavailable ({type(exc).__name__}: {exc}); using nccl", file=sys.stderr)
+                self.transport = "nccl"
+                self.layer = ExpertParallelMoE(self.gw, self.gws, self.dw, self.dws, experts)
         self.out = None
         a = tokens * topk
         self.flops_rank = 6.0 * a * hidden * inter      # expected share when routing is balanced
@@ -387,7 +400,7 @@ def run_moe(args, world, rank, device, peaks):
         "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate), bf16 activations", "data": "synthetic",
         "config": {"workload": "fused_moe_deepseek_v3_shape", "tokens_per_rank": wl.t, "hidden": wl.h,
                    "intermediate": wl.i, "experts": wl.e, "topk": wl.k, "experts_per_rank": wl.e_local,
-                   "parallelism": f"ep{world}" if world > 1 else "single", "l2": "256 MiB flush write between timed steps"},
+                   "parallelism": f"ep{world}" if world > 1 else "single", "exchange": wl.transport, "l2": "256 MiB flush write between timed steps"},
         "e2e": {"value": tokens_total / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": wl.h2d,
                 "d2h_bytes_per_step": wl.d2h, "ms_per_step": ms_e2e},
         "gpu_launches": int(launches_per_step * steps),

@@ -276,6 +276,36 @@ B200_NVFP4_API int b200_nvfp4_ep_unpack_rows(void* x_packed, void* x_scale, void
                                              void* topk_weights, const void* records, int rows,
                                              int hidden_size, int num_topk, b200_stream_t stream);
 
+/* The same hand-off over peer memory instead of a collective: every rank has a receive buffer of
+ * `world` slots of `slot_rows` wire records, an int32 count per slot, and a return buffer of `world`
+ * slots of `slot_rows` rows, all mapped into the peers' address spaces (peer_*[r] = rank r's buffer
+ * as this process addresses it). No counterpart in the reference.
+ *   ep_dispatch_p2p   ep_pack_rows, but each record is stored straight into slot `my_rank` of its
+ *                     destination rank, the per-destination counts likewise; ret_pos[t, r]
+ *                     (int32 [T, world]) receives the row of this rank's return buffer that the
+ *                     partial result of token t from rank r will occupy, or -1.
+ *   ep_unpack_slots   all world * slot_rows slot rows -> inputs of b200_nvfp4_fused_moe (rank_ep set);
+ *                     rows beyond a slot's count get expert id -1 everywhere.
+ *   ep_return_p2p     row (s, k) of `partial` [world * slot_rows, row_bytes] -> row (my_rank, k) of
+ *                     rank s's return buffer, for k < counts[s].
+ * The caller separates dispatch stores / reads and return stores / reads with a barrier over all
+ * ranks (the kernels themselves never wait on another GPU). num_tokens <= slot_rows. */
+B200_NVFP4_API int b200_nvfp4_ep_dispatch_p2p(const void* const* peer_records,
+                                              const void* const* peer_counts, void* ret_pos,
+                                              const void* x, const void* topk_ids,
+                                              const void* topk_weights, const void* send_pos,
+                                              const void* send_counts, const void* send_cu,
+                                              int my_rank, int world, int slot_rows, int num_tokens,
+                                              int hidden_size, int num_topk, int input_is_bf16,
+                                              b200_stream_t stream);
+B200_NVFP4_API int b200_nvfp4_ep_unpack_slots(void* x_packed, void* x_scale, void* topk_ids,
+                                              void* topk_weights, const void* records,
+                                              const void* counts, int world, int slot_rows,
+                                              int hidden_size, int num_topk, b200_stream_t stream);
+B200_NVFP4_API int b200_nvfp4_ep_return_p2p(const void* const* peer_ret, const void* partial,
+                                            const void* counts, int my_rank, int world,
+                                            int slot_rows, int row_bytes, b200_stream_t stream);
+
 /* Reads and clears the device word in which a kernel records a timed-out wait (every wait
  * inside the kernels is bounded). SYNCHRONISES the device. *code receives 0 when nothing
  * was recorded. No counterpart in the reference. */

@@ -169,6 +169,138 @@ ep_unpack_kernel(uint8_t* __restrict__ x_packed, uint8_t* __restrict__ x_scale, 
   }
 }
 
+// ---------------------------------------------------------------- peer-to-peer hand-off
+//
+// The same hand-off without a collective library in the data path: every rank owns a receive
+// buffer of `world` slots of `slot_rows` records (slot s belongs to source rank s) and a return
+// buffer of `world` slots of `slot_rows` FP16 rows (slot r holds what expert rank r sends back),
+// both mapped into every peer's address space. The pack kernel stores each record straight into
+// the destination rank's slot over NVLink, the return kernel stores each partial row straight
+// into its source's slot; counts travel the same way. Nothing is read back to the host and no
+// split sizes are needed: the positions inside a slot are the routing positions. The caller
+// separates the phases with a cross-GPU barrier (after the dispatch stores, after the return
+// stores). All peer accesses are plain global stores; nothing here waits on another GPU.
+struct PeerPointers {
+  uint8_t* p[kMaxWorld];
+};
+
+template <bool kBf16>
+__global__ void __launch_bounds__(256)
+ep_dispatch_p2p_kernel(PeerPointers peer_records, PeerPointers peer_counts, int* __restrict__ ret_pos,
+                       const void* __restrict__ x, const int* __restrict__ topk_ids,
+                       const float* __restrict__ topk_weights, const int* __restrict__ send_pos,
+                       const int* __restrict__ send_counts, const int* __restrict__ send_cu, int my_rank,
+                       int world, int slot_rows, int num_tokens, int hidden, int num_topk) {
+  const int lane = threadIdx.x & 31;
+  const int nkb = hidden >> 4;
+  const int groups_per_row = (nkb + 31) >> 5;
+  const long long rb = record_bytes(hidden, num_topk);
+  const int payload_bytes = hidden >> 1;
+  const long long items = static_cast<long long>(num_tokens) * groups_per_row;
+  const int warps_per_block = blockDim.x >> 5;
+  if (blockIdx.x == 0 && threadIdx.x < world)   // how many records each destination will find in my slot
+    reinterpret_cast<int*>(peer_counts.p[threadIdx.x])[my_rank] = send_counts[threadIdx.x];
+  for (long long item = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
+       item < items; item += static_cast<long long>(gridDim.x) * warps_per_block) {
+    const int t = static_cast<int>(item / groups_per_row);
+    const int group = static_cast<int>(item % groups_per_row);
+    const int kb = group * 32 + lane;
+    const bool live = kb < nkb;
+    uint32_t lo = 0, hi = 0;
+    uint8_t code = 0;
+    if (live) {
+      float v[16];
+      if constexpr (kBf16) {
+        load16_bf16(static_cast<const __nv_bfloat16*>(x) + static_cast<long long>(t) * hidden + kb * 16, v);
+      } else {
+        load16_f16(static_cast<const __half*>(x) + static_cast<long long>(t) * hidden + kb * 16, v);
+      }
+      code = quantize_block16(v, lo, hi);
+    }
+    uint32_t word = static_cast<uint32_t>(code) << (8 * (lane & 3));
+    word |= __shfl_xor_sync(0xffffffffu, word, 1);
+    word |= __shfl_xor_sync(0xffffffffu, word, 2);
+    for (int r = 0; r < world; ++r) {
+      const int pos = send_pos[static_cast<long long>(t) * world + r];
+      const int k = pos < 0 ? -1 : pos - send_cu[r];          // index inside my slot at rank r
+      if (group == 0 && lane == 0) ret_pos[static_cast<long long>(t) * world + r] = k < 0 ? -1 : r * slot_rows + k;
+      if (k < 0 || k >= slot_rows) continue;
+      uint8_t* rec = peer_records.p[r] + (static_cast<long long>(my_rank) * slot_rows + k) * rb;
+      if (live) {
+        *reinterpret_cast<uint2*>(rec + kb * 8) = make_uint2(lo, hi);
+        if ((lane & 3) == 0) *reinterpret_cast<uint32_t*>(rec + payload_bytes + kb) = word;
+      }
+      if (group == 0) {
+        int* rid = reinterpret_cast<int*>(rec + payload_bytes + nkb);
+        float* rw = reinterpret_cast<float*>(rec + payload_bytes + nkb + 4 * num_topk);
+        for (int j = lane; j < num_topk; j += 32) {
+          rid[j] = topk_ids[static_cast<long long>(t) * num_topk + j];
+          rw[j] = topk_weights[static_cast<long long>(t) * num_topk + j];
+        }
+      }
+    }
+  }
+}
+
+// Slot rows -> inputs of the routed layer over all world * slot_rows rows: rows a source did not
+// fill get expert id -1 in every position, so the routing ignores them.
+__global__ void __launch_bounds__(256)
+ep_unpack_slots_kernel(uint8_t* __restrict__ x_packed, uint8_t* __restrict__ x_scale, int* __restrict__ ids,
+                       float* __restrict__ weights, const uint8_t* __restrict__ records,
+                       const int* __restrict__ counts, int world, int slot_rows, int hidden, int num_topk) {
+  const int lane = threadIdx.x & 31;
+  const int nkb = hidden >> 4;
+  const int kt = (nkb + 3) >> 2;
+  const long long rb = record_bytes(hidden, num_topk);
+  const int payload_bytes = hidden >> 1;
+  const int warps_per_block = blockDim.x >> 5;
+  const int rows = world * slot_rows;
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
+    const int src_rank = row / slot_rows;
+    const bool valid = row - src_rank * slot_rows < counts[src_rank];
+    if (!valid) {
+      for (int j = lane; j < num_topk; j += 32) {
+        ids[static_cast<long long>(row) * num_topk + j] = -1;
+        weights[static_cast<long long>(row) * num_topk + j] = 0.0f;
+      }
+      continue;
+    }
+    const uint8_t* rec = records + static_cast<long long>(row) * rb;
+    const uint4* src = reinterpret_cast<const uint4*>(rec);
+    uint4* dst = reinterpret_cast<uint4*>(x_packed + static_cast<long long>(row) * payload_bytes);
+    for (int i = lane; i < (payload_bytes >> 4); i += 32) dst[i] = src[i];
+    uint8_t* s_row = x_scale + sf_offset(row, 0, kt);
+    for (int j = lane; j < kt; j += 32)
+      *reinterpret_cast<uint32_t*>(s_row + static_cast<long long>(j) * 512) =
+          *reinterpret_cast<const uint32_t*>(rec + payload_bytes + 4 * j);
+    const int* rid = reinterpret_cast<const int*>(rec + payload_bytes + nkb);
+    const float* rw = reinterpret_cast<const float*>(rec + payload_bytes + nkb + 4 * num_topk);
+    for (int j = lane; j < num_topk; j += 32) {
+      ids[static_cast<long long>(row) * num_topk + j] = rid[j];
+      weights[static_cast<long long>(row) * num_topk + j] = rw[j];
+    }
+  }
+}
+
+// Partial rows back to their sources: row (s, k) of my slots goes to row (my_rank, k) of rank s.
+__global__ void __launch_bounds__(256)
+ep_return_p2p_kernel(PeerPointers peer_ret, const uint8_t* __restrict__ partial, const int* __restrict__ counts,
+                     int my_rank, int world, int slot_rows, int row_bytes) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int rows = world * slot_rows;
+  const int vecs = row_bytes >> 4;
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
+    const int src_rank = row / slot_rows;
+    const int k = row - src_rank * slot_rows;
+    if (k >= counts[src_rank]) continue;
+    const uint4* s4 = reinterpret_cast<const uint4*>(partial + static_cast<long long>(row) * row_bytes);
+    uint4* d4 = reinterpret_cast<uint4*>(peer_ret.p[src_rank] +
+                                         (static_cast<long long>(my_rank) * slot_rows + k) * row_bytes);
+    for (int v = lane; v < vecs; v += 32) d4[v] = s4[v];
+  }
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int check_launch() {
@@ -248,6 +380,95 @@ int b200_nvfp4_ep_unpack_rows(void* x_packed, void* x_scale, void* topk_ids, voi
       static_cast<uint8_t*>(x_packed), static_cast<uint8_t*>(x_scale), static_cast<int*>(topk_ids),
       static_cast<float*>(topk_weights), static_cast<const uint8_t*>(records), rows, hidden_size,
       num_topk);
+  b200::count_launch();
+  return b200::check_launch();
+}
+
+int b200_nvfp4_ep_dispatch_p2p(const void* const* peer_records, const void* const* peer_counts, void* ret_pos,
+                               const void* x, const void* topk_ids, const void* topk_weights,
+                               const void* send_pos, const void* send_counts, const void* send_cu, int my_rank,
+                               int world, int slot_rows, int num_tokens, int hidden_size, int num_topk,
+                               int input_is_bf16, b200_stream_t stream) {
+  if (peer_records == nullptr || peer_counts == nullptr || ret_pos == nullptr || x == nullptr ||
+      topk_ids == nullptr || topk_weights == nullptr || send_pos == nullptr || send_counts == nullptr ||
+      send_cu == nullptr || world <= 0 || world > b200::kMaxWorld || my_rank < 0 || my_rank >= world ||
+      slot_rows <= 0 || num_tokens <= 0 || num_tokens > slot_rows || hidden_size <= 0 ||
+      (hidden_size % 64) != 0 || num_topk <= 0 || !b200::aligned16(x)) {
+    return B200_NVFP4_INVALID_ARGUMENT;
+  }
+  b200::PeerPointers rec{}, cnt{};
+  for (int r = 0; r < world; ++r) {
+    if (peer_records[r] == nullptr || peer_counts[r] == nullptr || !b200::aligned16(peer_records[r]))
+      return B200_NVFP4_INVALID_ARGUMENT;
+    rec.p[r] = static_cast<uint8_t*>(const_cast<void*>(peer_records[r]));
+    cnt.p[r] = static_cast<uint8_t*>(const_cast<void*>(peer_counts[r]));
+  }
+  const b200::DeviceInfo& dev = b200::current_device_info();
+  if (!dev.ok) return B200_NVFP4_CUDA_ERROR;
+  const long long groups_per_row = ((hidden_size >> 4) + 31) >> 5;
+  long long blocks = (static_cast<long long>(num_tokens) * groups_per_row + 7) / 8;
+  const long long max_blocks = static_cast<long long>(dev.sm_count) * 8;
+  if (blocks > max_blocks) blocks = max_blocks;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  auto* ids = static_cast<const int*>(topk_ids);
+  auto* wts = static_cast<const float*>(topk_weights);
+  if (input_is_bf16) {
+    b200::ep_dispatch_p2p_kernel<true><<<static_cast<int>(blocks), 256, 0, s>>>(
+        rec, cnt, static_cast<int*>(ret_pos), x, ids, wts, static_cast<const int*>(send_pos),
+        static_cast<const int*>(send_counts), static_cast<const int*>(send_cu), my_rank, world, slot_rows,
+        num_tokens, hidden_size, num_topk);
+  } else {
+    b200::ep_dispatch_p2p_kernel<false><<<static_cast<int>(blocks), 256, 0, s>>>(
+        rec, cnt, static_cast<int*>(ret_pos), x, ids, wts, static_cast<const int*>(send_pos),
+        static_cast<const int*>(send_counts), static_cast<const int*>(send_cu), my_rank, world, slot_rows,
+        num_tokens, hidden_size, num_topk);
+  }
+  b200::count_launch();
+  return b200::check_launch();
+}
+
+int b200_nvfp4_ep_unpack_slots(void* x_packed, void* x_scale, void* topk_ids, void* topk_weights,
+                               const void* records, const void* counts, int world, int slot_rows,
+                               int hidden_size, int num_topk, b200_stream_t stream) {
+  if (x_packed == nullptr || x_scale == nullptr || topk_ids == nullptr || topk_weights == nullptr ||
+      records == nullptr || counts == nullptr || world <= 0 || world > b200::kMaxWorld || slot_rows <= 0 ||
+      hidden_size <= 0 || (hidden_size % 64) != 0 || num_topk <= 0 || !b200::aligned16(x_packed) ||
+      !b200::aligned16(x_scale) || !b200::aligned16(records)) {
+    return B200_NVFP4_INVALID_ARGUMENT;
+  }
+  const b200::DeviceInfo& dev = b200::current_device_info();
+  if (!dev.ok) return B200_NVFP4_CUDA_ERROR;
+  long long blocks = (static_cast<long long>(world) * slot_rows + 7) / 8;
+  const long long max_blocks = static_cast<long long>(dev.sm_count) * 8;
+  if (blocks > max_blocks) blocks = max_blocks;
+  b200::ep_unpack_slots_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint8_t*>(x_packed), static_cast<uint8_t*>(x_scale), static_cast<int*>(topk_ids),
+      static_cast<float*>(topk_weights), static_cast<const uint8_t*>(records), static_cast<const int*>(counts),
+      world, slot_rows, hidden_size, num_topk);
+  b200::count_launch();
+  return b200::check_launch();
+}
+
+int b200_nvfp4_ep_return_p2p(const void* const* peer_ret, const void* partial, const void* counts, int my_rank,
+                             int world, int slot_rows, int row_bytes, b200_stream_t stream) {
+  if (peer_ret == nullptr || partial == nullptr || counts == nullptr || world <= 0 ||
+      world > b200::kMaxWorld || my_rank < 0 || my_rank >= world || slot_rows <= 0 || row_bytes <= 0 ||
+      (row_bytes % 16) != 0 || !b200::aligned16(partial)) {
+    return B200_NVFP4_INVALID_ARGUMENT;
+  }
+  b200::PeerPointers ret{};
+  for (int r = 0; r < world; ++r) {
+    if (peer_ret[r] == nullptr || !b200::aligned16(peer_ret[r])) return B200_NVFP4_INVALID_ARGUMENT;
+    ret.p[r] = static_cast<uint8_t*>(const_cast<void*>(peer_ret[r]));
+  }
+  const b200::DeviceInfo& dev = b200::current_device_info();
+  if (!dev.ok) return B200_NVFP4_CUDA_ERROR;
+  long long blocks = (static_cast<long long>(world) * slot_rows + 7) / 8;
+  const long long max_blocks = static_cast<long long>(dev.sm_count) * 8;
+  if (blocks > max_blocks) blocks = max_blocks;
+  b200::ep_return_p2p_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      ret, static_cast<const uint8_t*>(partial), static_cast<const int*>(counts), my_rank, world, slot_rows,
+      row_bytes);
   b200::count_launch();
   return b200::check_launch();
 }

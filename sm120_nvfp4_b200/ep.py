@@ -21,12 +21,20 @@ torch.distributed (NCCL over NVLink / NVSwitch, gloo on CPU) is the transport; t
 of the row exchanges are read back to the host once per call, as in the reference script. All
 kernels read and write local HBM only.
 
+Two transports carry the records and the partial rows. "nccl": `all_to_all_single` (one host
+read-back of the split sizes per call, as in the reference script). "p2p": no collective library
+and no host read-back in the data path - every rank owns slotted receive / return buffers in
+symmetric memory (torch.distributed._symmetric_memory, CUDA IPC over NVLink) and the pack /
+return kernels store straight into the peer's slots (b200_nvfp4_ep_dispatch_p2p / _ep_unpack_slots
+/ _ep_return_p2p), separated by two cross-GPU barriers per layer.
+
 The compute steps go through a small backend object so that the host logic (splits, ordering,
 the two exchanges) can be exercised on CPU ranks with a checker backend supplied by the tests;
 the default backend calls the C ABI and needs a CUDA device.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Optional
 
 import torch
@@ -106,6 +114,35 @@ class CudaBackend:
         return out
 
 
+class _PeerBuffers:
+    """Slotted receive / return buffers of one rank, visible to every peer (symmetric memory)."""
+
+    def __init__(self, group, world: int, slot_rows: int, hidden: int, topk: int, device):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.world, self.slot_rows, self.hidden, self.topk = world, slot_rows, hidden, topk
+        self.rb = record_bytes(hidden, topk)
+        rows = world * slot_rows
+        rec_bytes = rows * self.rb
+        self.cnt_off = (rec_bytes + 255) // 256 * 256
+        self.ret_off = self.cnt_off + 256
+        total = self.ret_off + rows * hidden * 2
+        self.buf = symm_mem.empty(total, dtype=torch.uint8, device=device)
+        self.handle = symm_mem.rendezvous(self.buf, group=group if group is not None else dist.group.WORLD)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        arr = ctypes.c_void_p * world
+        self.peer_rec = arr(*ptrs)
+        self.peer_cnt = arr(*[p + self.cnt_off for p in ptrs])
+        self.peer_ret = arr(*[p + self.ret_off for p in ptrs])
+        self.rec = self.buf[:rec_bytes].view(rows, self.rb)
+        self.cnt = self.buf[self.cnt_off:self.cnt_off + 4 * world].view(torch.int32)
+        self.ret = self.buf[self.ret_off:total].view(torch.float16).view(rows, hidden)
+        self.buf.zero_()
+        self.handle.barrier(channel=0)
+
+    def barrier(self):
+        self.handle.barrier(channel=0)
+
+
 class ExpertParallelMoE:
     """One MoE layer whose experts are sharded over the ranks of `group`.
 
@@ -116,7 +153,8 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, gate_up_weight, gate_up_weight_scale, down_weight, down_weight_scale, num_experts_total: int,
-                 group: Optional[dist.ProcessGroup] = None, backend=None):
+                 group: Optional[dist.ProcessGroup] = None, backend=None, transport: str = "nccl",
+                 max_tokens: int = 0, num_topk: int = 0):
         self.gw, self.gws, self.dw, self.dws = gate_up_weight, gate_up_weight_scale, down_weight, down_weight_scale
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -128,6 +166,15 @@ class ExpertParallelMoE:
         self.backend = backend if backend is not None else CudaBackend()
         self.last_bytes = {"dispatch": 0, "combine": 0}
         self._ones = None
+        if transport not in ("nccl", "p2p"):
+            raise ValueError("transport must be 'nccl' or 'p2p'")
+        self.transport = transport
+        self.peers = None
+        if transport == "p2p":
+            if max_tokens <= 0 or num_topk <= 0:
+                raise ValueError("the p2p transport needs max_tokens (tokens per rank per call) and num_topk")
+            hidden = gate_up_weight.shape[2] * 2
+            self.peers = _PeerBuffers(group, self.world, int(max_tokens), hidden, int(num_topk), gate_up_weight.device)
 
     def _all_to_all_rows(self, send, send_splits, recv_splits):
         recv = torch.empty((sum(recv_splits), send.shape[1]), dtype=send.dtype, device=send.device)
@@ -138,7 +185,45 @@ class ExpertParallelMoE:
         return recv
 
     @torch.no_grad()
+    def _forward_p2p(self, x, topk_ids, topk_weights, out_bf16: bool):
+        w, be, pb = self.world, self.backend, self.peers
+        t, hidden = x.shape
+        k = topk_ids.shape[1]
+        if t > pb.slot_rows or k != pb.topk or hidden != pb.hidden:
+            raise ValueError("call does not fit the peer buffers this layer was built with")
+        L = _lib.lib()
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        dest = be.dest_ranks(topk_ids, self.e_local, w)
+        send_pos, send_counts, send_cu = be.route(dest, w)
+        ret_pos = torch.empty((t, w), dtype=torch.int32, device=x.device)
+        # records and counts straight into the destination ranks' slots
+        _lib.check(L.b200_nvfp4_ep_dispatch_p2p(pb.peer_rec, pb.peer_cnt, ret_pos.data_ptr(), x.data_ptr(),
+                                                topk_ids.data_ptr(), topk_weights.data_ptr(), send_pos.data_ptr(),
+                                                send_counts.data_ptr(), send_cu.data_ptr(), self.rank, w, pb.slot_rows,
+                                                t, hidden, k, int(x.dtype == torch.bfloat16), stream), "ep_dispatch_p2p")
+        pb.barrier()
+        rows = w * pb.slot_rows
+        m_pad = (rows + 127) // 128 * 128
+        xq = torch.empty((rows, hidden // 2), dtype=torch.uint8, device=x.device)
+        xs = torch.empty(m_pad * scale_k_padded(hidden), dtype=torch.uint8, device=x.device)
+        ids = torch.empty((rows, k), dtype=torch.int32, device=x.device)
+        wts = torch.empty((rows, k), dtype=torch.float32, device=x.device)
+        _lib.check(L.b200_nvfp4_ep_unpack_slots(xq.data_ptr(), xs.data_ptr(), ids.data_ptr(), wts.data_ptr(),
+                                                pb.rec.data_ptr(), pb.cnt.data_ptr(), w, pb.slot_rows, hidden, k,
+                                                stream), "ep_unpack_slots")
+        part = be.local_moe(xq, xs, ids, wts, self.gw, self.gws, self.dw, self.dws, self.rank, self.num_experts_total)
+        # partial rows straight into their sources' return slots
+        _lib.check(L.b200_nvfp4_ep_return_p2p(pb.peer_ret, part.data_ptr(), pb.cnt.data_ptr(), self.rank, w,
+                                              pb.slot_rows, hidden * 2, stream), "ep_return_p2p")
+        pb.barrier()
+        if self._ones is None or self._ones.shape != (t, w) or self._ones.device != x.device:
+            self._ones = torch.ones((t, w), dtype=torch.float32, device=x.device)
+        return be.reduce(pb.ret, ret_pos, self._ones, out_bf16)
+
+    @torch.no_grad()
     def forward(self, x, topk_ids, topk_weights, out_bf16: bool = True):
+        if self.transport == "p2p":
+            return self._forward_p2p(x, topk_ids, topk_weights, out_bf16)
         w, be = self.world, self.backend
         t, hidden = x.shape
         k = topk_ids.shape[1]
