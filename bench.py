@@ -328,15 +328,24 @@ class MoeWorkload:
         self.transport = os.environ.get("B200_NVFP4_EP_TRANSPORT", "p2p") if world > 1 else "none"
         self.layer = None
         if world > 1:
+            import torch.distributed as dist
+            layer, err = None, None
             try:
-                self.layer = ExpertParallelMoE(self.gw, self.gws, self.dw, self.dws, experts, transport=self.transport,
-                                               max_tokens=tokens, num_topk=topk)
-            except Exception as exc:   # no symmetric memory on this box: the all-to-all transport
+                layer = ExpertParallelMoE(self.gw, self.gws, self.dw, self.dws, experts, transport=self.transport,
+                                          max_tokens=tokens, num_topk=topk)
+            except Exception as exc:   # e.g. no symmetric memory on this box
                 if self.transport != "p2p":
                     raise
-                print(f"[bench] p2p transport unavailable ({type(exc).__name__}: {exc}); using nccl", file=sys.stderr)
+                err = f"{type(exc).__name__}: {exc}"
+            # every rank must use the same transport: agree on the outcome
+            ok = torch.tensor([0 if layer is None else 1], dtype=torch.int32, device=device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                if rank == 0:
+                    print(f"[bench] p2p transport unavailable on some rank ({err}); using nccl", file=sys.stderr)
                 self.transport = "nccl"
-                self.layer = ExpertParallelMoE(self.gw, self.gws, self.dw, self.dws, experts)
+                layer = ExpertParallelMoE(self.gw, self.gws, self.dw, self.dws, experts)
+            self.layer = layer
         self.out = None
         a = tokens * topk
         self.flops_rank = 6.0 * a * hidden * inter      # expected share when routing is balanced
