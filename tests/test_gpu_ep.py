@@ -80,3 +80,68 @@ def test_layer_on_one_rank_matches_oracle(backend):
     xb = x.view(torch.int16).numpy().view(np.uint16)
     want = expected_ep_output(xb, ids, w, gw, gws, dw, dws, 1)
     check_gemm_parity(out.cpu().numpy(), want.astype(np.float32))
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_peer_memory_hand_off_emulated_on_one_gpu(backend, world):
+    # All ranks of the peer-memory transport on one GPU: every "rank" has its own slotted buffers,
+    # the peer pointer tables point at the other ranks' buffers on the same device, and the phases
+    # run rank after rank where the real layer has its two barriers. Checks the slot addressing of
+    # dispatch / unpack / return for more than two ranks against the oracle's per-rank composition.
+    import ctypes
+    from sm120_nvfp4_b200 import _lib, ops
+    from sm120_nvfp4_b200.ep import record_bytes
+    L = _lib.lib()
+    experts, hidden, inter, topk, tokens, slot = 2 * world, 128, 64, 3, 29, 32
+    e_local = experts // world
+    gw = np.empty((experts, 2 * inter, hidden // 2), np.uint8)
+    gws = np.empty((experts, oracle.scale_region_bytes(2 * inter, hidden)), np.uint8)
+    dw = np.empty((experts, hidden, inter // 2), np.uint8)
+    dws = np.empty((experts, oracle.scale_region_bytes(hidden, inter)), np.uint8)
+    for e in range(experts):
+        gw[e], gws[e] = randn_quantized(2 * inter, hidden, 10 + 2 * e, 0.5)
+        dw[e], dws[e] = randn_quantized(hidden, inter, 11 + 2 * e, 0.5)
+    rb = record_bytes(hidden, topk)
+    rows = world * slot
+    rec = [torch.zeros((rows, rb), dtype=torch.uint8, device="cuda") for _ in range(world)]
+    cnt = [torch.zeros(world, dtype=torch.int32, device="cuda") for _ in range(world)]
+    ret = [torch.zeros((rows, hidden), dtype=torch.float16, device="cuda") for _ in range(world)]
+    arr = ctypes.c_void_p * world
+    peer_rec, peer_cnt, peer_ret = (arr(*[t.data_ptr() for t in ts]) for ts in (rec, cnt, ret))
+    stream = torch.cuda.current_stream().cuda_stream
+    inputs, ret_pos = [], []
+    for r in range(world):                                   # phase 1: every rank dispatches
+        x = _bf16_rows(tokens, hidden, 100 + r).cuda()
+        ids, w = topk_routing(tokens, experts, topk, 200 + r)
+        ids_t, w_t = torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()
+        dest = backend.dest_ranks(ids_t, e_local, world)
+        pos, counts, cu = backend.route(dest, world)
+        rp = torch.empty((tokens, world), dtype=torch.int32, device="cuda")
+        assert L.b200_nvfp4_ep_dispatch_p2p(peer_rec, peer_cnt, rp.data_ptr(), x.data_ptr(), ids_t.data_ptr(),
+                                            w_t.data_ptr(), pos.data_ptr(), counts.data_ptr(), cu.data_ptr(), r, world,
+                                            slot, tokens, hidden, topk, 1, stream) == 0
+        inputs.append((x, ids, w))
+        ret_pos.append(rp)
+    for r in range(world):                                   # phase 2: every rank computes and returns
+        xq = torch.empty((rows, hidden // 2), dtype=torch.uint8, device="cuda")
+        xs = torch.empty(((rows + 127) // 128 * 128) * ops.scale_k_padded(hidden), dtype=torch.uint8, device="cuda")
+        rid = torch.empty((rows, topk), dtype=torch.int32, device="cuda")
+        rw = torch.empty((rows, topk), dtype=torch.float32, device="cuda")
+        assert L.b200_nvfp4_ep_unpack_slots(xq.data_ptr(), xs.data_ptr(), rid.data_ptr(), rw.data_ptr(),
+                                            rec[r].data_ptr(), cnt[r].data_ptr(), world, slot, hidden, topk, stream) == 0
+        sl = slice(r * e_local, (r + 1) * e_local)
+        part = ops.fused_moe(xq, xs, torch.from_numpy(gw[sl].copy()).cuda(), torch.from_numpy(gws[sl].copy()).cuda(),
+                             torch.from_numpy(dw[sl].copy()).cuda(), torch.from_numpy(dws[sl].copy()).cuda(), rid, rw,
+                             ep_rank=r, num_experts=experts)
+        assert L.b200_nvfp4_ep_return_p2p(peer_ret, part.data_ptr(), cnt[r].data_ptr(), r, world, slot, hidden * 2,
+                                          stream) == 0
+    ones = torch.ones((tokens, world), dtype=torch.float32, device="cuda")
+    for r in range(world):                                   # phase 3: every rank sums its partial rows
+        out = backend.reduce(ret[r], ret_pos[r], ones, False)
+        torch.cuda.synchronize()
+        x, ids, w = inputs[r]
+        xb = x.cpu().view(torch.int16).numpy().view(np.uint16)
+        want = expected_ep_output(xb, ids, w, gw, gws, dw, dws, world).astype(np.float32)
+        got = out.cpu().numpy().astype(np.float32)
+        frob = np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)
+        assert frob < 2e-2, (r, frob)
