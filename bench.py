@@ -270,7 +270,7 @@ def run_gemm(args, world, rank, device, peaks):
     # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from one ncu capture of this
     # kernel on this workload (profiles/: the DRAM-traffic summary of the 8192^3 case and the
     # full capture of the 4096 x 4096 x 8192 case); not captured for the sharded workload
-    ncu_traffic = {"gemm8192": 266.65e6, "gemm4096": 42.6e6}.get(args.workload) if world == 1 else None
+    ncu_traffic = {"gemm8192": 268.56e6, "gemm4096": 42.3e6}.get(args.workload) if world == 1 else None
     line = {
         "metric": "NVFP4 GEMM TFLOPS (% FP4 peak); fused-MoE tokens/s at 1/2/4/8 B200",
         "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
