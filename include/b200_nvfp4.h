@@ -305,6 +305,16 @@ B200_NVFP4_API int b200_nvfp4_ep_unpack_slots(void* x_packed, void* x_scale, voi
 B200_NVFP4_API int b200_nvfp4_ep_return_p2p(const void* const* peer_ret, const void* partial,
                                             const void* counts, int my_rank, int world,
                                             int slot_rows, int row_bytes, b200_stream_t stream);
+/* ep_return_p2p fused with the reduce step that produces `partial`: the weighted sum over a slot
+ * row's local experts (b200_nvfp4_moe_reduce arithmetic, FP16 result, no shared-expert term) is
+ * stored straight into the source rank's return slot. down_output / topk_pos / topk_scale are the
+ * routed layer's intermediates over all world * slot_rows slot rows. */
+B200_NVFP4_API int b200_nvfp4_ep_reduce_return_p2p(const void* const* peer_ret,
+                                                   const void* down_output, const void* topk_pos,
+                                                   const void* topk_scale, const void* counts,
+                                                   int my_rank, int world, int slot_rows,
+                                                   int hidden_size, int num_topk,
+                                                   b200_stream_t stream);
 
 /* Reads and clears the device word in which a kernel records a timed-out wait (every wait
  * inside the kernels is bounded). SYNCHRONISES the device. *code receives 0 when nothing

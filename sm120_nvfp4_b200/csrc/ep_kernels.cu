@@ -301,6 +301,55 @@ ep_return_p2p_kernel(PeerPointers peer_ret, const uint8_t* __restrict__ partial,
   }
 }
 
+// The weighted sum over a received token's local experts (the reduce step of the routed layer,
+// src/fused_moe/reduce.cu:12-35: FP32 accumulation in route order, one rounding to FP16) written
+// straight into the source rank's return slot instead of a local matrix: row (s, k) of the slot
+// space -> row (my_rank, k) of rank s. Rows beyond a slot's count are skipped.
+__global__ void __launch_bounds__(256)
+ep_reduce_return_p2p_kernel(PeerPointers peer_ret, const __half* __restrict__ down_output,
+                            const int* __restrict__ topk_pos, const float* __restrict__ topk_scale,
+                            const int* __restrict__ counts, int my_rank, int world, int slot_rows, int hidden,
+                            int num_topk) {
+  const int chunks = hidden >> 3;
+  const long long items = static_cast<long long>(world) * slot_rows * chunks;
+  for (long long item = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; item < items;
+       item += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(item / chunks);
+    const int col = static_cast<int>(item % chunks) * 8;
+    const int src_rank = row / slot_rows;
+    const int k = row - src_rank * slot_rows;
+    if (k >= counts[src_rank]) continue;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+    const int* pos = topk_pos + static_cast<long long>(row) * num_topk;
+    const float* wts = topk_scale + static_cast<long long>(row) * num_topk;
+    for (int r = 0; r < num_topk; ++r) {
+      const int drow = pos[r];
+      if (drow < 0) continue;
+      const float wt = wts[r];
+      const uint4 d = *reinterpret_cast<const uint4*>(down_output + static_cast<long long>(drow) * hidden + col);
+      const uint32_t w[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+        acc[2 * i] = __fmaf_rn(__low2float(h), wt, acc[2 * i]);
+        acc[2 * i + 1] = __fmaf_rn(__high2float(h), wt, acc[2 * i + 1]);
+      }
+    }
+    uint4 o;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __half2 h = __floats2half2_rn(acc[2 * i], acc[2 * i + 1]);
+      ow[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    __half* dst = reinterpret_cast<__half*>(peer_ret.p[src_rank]) +
+                  (static_cast<long long>(my_rank) * slot_rows + k) * hidden + col;
+    *reinterpret_cast<uint4*>(dst) = o;
+  }
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int check_launch() {
@@ -469,6 +518,34 @@ int b200_nvfp4_ep_return_p2p(const void* const* peer_ret, const void* partial, c
   b200::ep_return_p2p_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       ret, static_cast<const uint8_t*>(partial), static_cast<const int*>(counts), my_rank, world, slot_rows,
       row_bytes);
+  b200::count_launch();
+  return b200::check_launch();
+}
+
+int b200_nvfp4_ep_reduce_return_p2p(const void* const* peer_ret, const void* down_output, const void* topk_pos,
+                                    const void* topk_scale, const void* counts, int my_rank, int world,
+                                    int slot_rows, int hidden_size, int num_topk, b200_stream_t stream) {
+  if (peer_ret == nullptr || down_output == nullptr || topk_pos == nullptr || topk_scale == nullptr ||
+      counts == nullptr || world <= 0 || world > b200::kMaxWorld || my_rank < 0 || my_rank >= world ||
+      slot_rows <= 0 || hidden_size <= 0 || (hidden_size % 8) != 0 || num_topk <= 0 ||
+      !b200::aligned16(down_output)) {
+    return B200_NVFP4_INVALID_ARGUMENT;
+  }
+  b200::PeerPointers ret{};
+  for (int r = 0; r < world; ++r) {
+    if (peer_ret[r] == nullptr || !b200::aligned16(peer_ret[r])) return B200_NVFP4_INVALID_ARGUMENT;
+    ret.p[r] = static_cast<uint8_t*>(const_cast<void*>(peer_ret[r]));
+  }
+  const b200::DeviceInfo& dev = b200::current_device_info();
+  if (!dev.ok) return B200_NVFP4_CUDA_ERROR;
+  const long long items = static_cast<long long>(world) * slot_rows * (hidden_size >> 3);
+  long long blocks = (items + 255) / 256;
+  const long long max_blocks = static_cast<long long>(dev.sm_count) * 16;
+  if (blocks > max_blocks) blocks = max_blocks;
+  b200::ep_reduce_return_p2p_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      ret, static_cast<const __half*>(down_output), static_cast<const int*>(topk_pos),
+      static_cast<const float*>(topk_scale), static_cast<const int*>(counts), my_rank, world, slot_rows,
+      hidden_size, num_topk);
   b200::count_launch();
   return b200::check_launch();
 }

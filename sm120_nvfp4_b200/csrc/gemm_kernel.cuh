@@ -101,7 +101,11 @@ struct GemmParams {
   uint8_t* q_out;             // packed E2M1 [rows, I/2]
   uint8_t* q_scale;           // UE4M3 scale regions, one per group, indexed by the row inside the group
   long long q_scale_group_stride;
-  int debug;                  // bit 64: record time stamps into `trace` (0 in production)
+  // Debug switches (environment variable B200_NVFP4_DEBUG, 0 in production). Bits 1, 2, 4 and 8
+  // switch parts of the kernel off to find what bounds it - results are then wrong by design:
+  // 1 no MMAs (data path only), 2 no operand loads (barriers only), 4 no tensor-memory stores of
+  // the scales, 8 no scale loads. Bit 64 records time stamps into `trace`.
+  int debug;
   unsigned long long* trace;  // optional time-stamp buffer (debug bit 64), else nullptr
 };
 

@@ -154,11 +154,15 @@ class ExpertParallelMoE:
 
     def __init__(self, gate_up_weight, gate_up_weight_scale, down_weight, down_weight_scale, num_experts_total: int,
                  group: Optional[dist.ProcessGroup] = None, backend=None, transport: str = "nccl",
-                 max_tokens: int = 0, num_topk: int = 0):
+                 max_tokens: int = 0, num_topk: int = 0, emulate=None):
         self.gw, self.gws, self.dw, self.dws = gate_up_weight, gate_up_weight_scale, down_weight, down_weight_scale
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if emulate is not None:
+            # (world, rank, peers): one process plays several ranks of the p2p transport, with a
+            # peers object whose pointer tables address the other emulated ranks' buffers
+            self.world, self.rank = int(emulate[0]), int(emulate[1])
         self.num_experts_total = int(num_experts_total)
         self.e_local = gate_up_weight.shape[0]
         if self.e_local * self.world != self.num_experts_total:
@@ -170,7 +174,9 @@ class ExpertParallelMoE:
             raise ValueError("transport must be 'nccl' or 'p2p'")
         self.transport = transport
         self.peers = None
-        if transport == "p2p":
+        if emulate is not None:
+            self.peers = emulate[2]
+        elif transport == "p2p":
             if max_tokens <= 0 or num_topk <= 0:
                 raise ValueError("the p2p transport needs max_tokens (tokens per rank per call) and num_topk")
             hidden = gate_up_weight.shape[2] * 2
@@ -184,8 +190,37 @@ class ExpertParallelMoE:
             dist.all_to_all_single(recv, send, recv_splits, send_splits, group=self.group)
         return recv
 
+    def _p2p_workspace(self, rows: int, hidden: int, k: int, device):
+        """Intermediates of the routed layer over all slot rows, allocated once per layer: the slots
+        have a fixed capacity, so the sizes never change."""
+        if getattr(self, "_ws", None) is not None:
+            return self._ws
+        inter = self.gw.shape[1] // 2
+        total = rows * k
+        in_pad = (rows + 127) // 128 * 128
+        m_pad = in_pad          # a token reaches an expert at most once: no expert sees more rows than there are slots
+        u8 = dict(dtype=torch.uint8, device=device)
+        i32 = dict(dtype=torch.int32, device=device)
+        f16 = dict(dtype=torch.float16, device=device)
+        self._ws = {
+            "inter": inter, "m_pad": m_pad, "in_pad": in_pad,
+            "xq": torch.empty((rows, hidden // 2), **u8), "xs": torch.empty(in_pad * scale_k_padded(hidden), **u8),
+            "ids": torch.empty((rows, k), **i32), "wts": torch.empty((rows, k), dtype=torch.float32, device=device),
+            "gin": torch.empty((total, hidden // 2), **u8),
+            "gin_s": torch.empty((self.e_local, m_pad * scale_k_padded(hidden)), **u8),
+            "gout": torch.empty((total, 2 * inter), **f16), "din": torch.empty((total, inter // 2), **u8),
+            "din_s": torch.empty((self.e_local, m_pad * scale_k_padded(inter)), **u8),
+            "dout": torch.empty((total, hidden), **f16), "pos": torch.empty((rows, k), **i32),
+            "seq": torch.empty(self.e_local, **i32), "cu": torch.empty(self.e_local + 1, **i32),
+        }
+        return self._ws
+
+    # The p2p layer in three phases; between them every rank passes a barrier. They are separate
+    # methods so that a single process can step several emulated ranks through them in turn.
     @torch.no_grad()
-    def _forward_p2p(self, x, topk_ids, topk_weights, out_bf16: bool):
+    def p2p_dispatch(self, x, topk_ids, topk_weights):
+        """Phase 1: quantise this rank's tokens and store their records into the destination ranks'
+        slots. Returns ret_pos [T, world]: where each token's partial rows will come back."""
         w, be, pb = self.world, self.backend, self.peers
         t, hidden = x.shape
         k = topk_ids.shape[1]
@@ -196,29 +231,63 @@ class ExpertParallelMoE:
         dest = be.dest_ranks(topk_ids, self.e_local, w)
         send_pos, send_counts, send_cu = be.route(dest, w)
         ret_pos = torch.empty((t, w), dtype=torch.int32, device=x.device)
-        # records and counts straight into the destination ranks' slots
         _lib.check(L.b200_nvfp4_ep_dispatch_p2p(pb.peer_rec, pb.peer_cnt, ret_pos.data_ptr(), x.data_ptr(),
                                                 topk_ids.data_ptr(), topk_weights.data_ptr(), send_pos.data_ptr(),
                                                 send_counts.data_ptr(), send_cu.data_ptr(), self.rank, w, pb.slot_rows,
                                                 t, hidden, k, int(x.dtype == torch.bfloat16), stream), "ep_dispatch_p2p")
-        pb.barrier()
+        return ret_pos
+
+    @torch.no_grad()
+    def p2p_compute_and_return(self):
+        """Phase 2: the routed layer over this rank's experts on everything its slots received, the
+        partial rows stored into the source ranks' return slots."""
+        w, pb = self.world, self.peers
+        hidden, k = pb.hidden, pb.topk
+        L = _lib.lib()
+        device = pb.rec.device
+        stream = torch.cuda.current_stream(device).cuda_stream
         rows = w * pb.slot_rows
-        m_pad = (rows + 127) // 128 * 128
-        xq = torch.empty((rows, hidden // 2), dtype=torch.uint8, device=x.device)
-        xs = torch.empty(m_pad * scale_k_padded(hidden), dtype=torch.uint8, device=x.device)
-        ids = torch.empty((rows, k), dtype=torch.int32, device=x.device)
-        wts = torch.empty((rows, k), dtype=torch.float32, device=x.device)
-        _lib.check(L.b200_nvfp4_ep_unpack_slots(xq.data_ptr(), xs.data_ptr(), ids.data_ptr(), wts.data_ptr(),
-                                                pb.rec.data_ptr(), pb.cnt.data_ptr(), w, pb.slot_rows, hidden, k,
-                                                stream), "ep_unpack_slots")
-        part = be.local_moe(xq, xs, ids, wts, self.gw, self.gws, self.dw, self.dws, self.rank, self.num_experts_total)
-        # partial rows straight into their sources' return slots
-        _lib.check(L.b200_nvfp4_ep_return_p2p(pb.peer_ret, part.data_ptr(), pb.cnt.data_ptr(), self.rank, w,
-                                              pb.slot_rows, hidden * 2, stream), "ep_return_p2p")
-        pb.barrier()
-        if self._ones is None or self._ones.shape != (t, w) or self._ones.device != x.device:
-            self._ones = torch.ones((t, w), dtype=torch.float32, device=x.device)
-        return be.reduce(pb.ret, ret_pos, self._ones, out_bf16)
+        ws = self._p2p_workspace(rows, hidden, k, device)
+        _lib.check(L.b200_nvfp4_ep_unpack_slots(ws["xq"].data_ptr(), ws["xs"].data_ptr(), ws["ids"].data_ptr(),
+                                                ws["wts"].data_ptr(), pb.rec.data_ptr(), pb.cnt.data_ptr(), w,
+                                                pb.slot_rows, hidden, k, stream), "ep_unpack_slots")
+        # the routed layer stage by stage (what b200_nvfp4_fused_moe runs), with its last step - the
+        # weighted sum over a token's local experts - storing straight into the source ranks' slots
+        inter, total, m_pad = ws["inter"], rows * k, ws["m_pad"]
+        avg = max(1, total // self.num_experts_total)
+        _lib.check(L.b200_nvfp4_moe_count_and_gather(
+            ws["gin"].data_ptr(), ws["gin_s"].data_ptr(), ws["xq"].data_ptr(), ws["xs"].data_ptr(), ws["ids"].data_ptr(),
+            ws["pos"].data_ptr(), ws["seq"].data_ptr(), ws["cu"].data_ptr(), rows, hidden, k, self.e_local, self.rank,
+            ws["in_pad"], m_pad, 0, stream), "moe_count_and_gather")
+        _lib.check(L.b200_nvfp4_grouped_gemm(
+            ws["gout"].data_ptr(), ws["gin"].data_ptr(), self.gw.data_ptr(), ws["seq"].data_ptr(), ws["cu"].data_ptr(),
+            ws["gin_s"].data_ptr(), self.gws.data_ptr(), None, None, None, self.e_local, total, 2 * inter, hidden, m_pad,
+            avg, 1, None, stream), "grouped_gemm (gate/up)")
+        _lib.check(L.b200_nvfp4_moe_act_mul_and_quant(
+            ws["din"].data_ptr(), ws["din_s"].data_ptr(), ws["gout"].data_ptr(), ws["seq"].data_ptr(), ws["cu"].data_ptr(),
+            self.e_local, total, m_pad, inter, 0, stream), "moe_act_mul_and_quant")
+        _lib.check(L.b200_nvfp4_grouped_gemm(
+            ws["dout"].data_ptr(), ws["din"].data_ptr(), self.dw.data_ptr(), ws["seq"].data_ptr(), ws["cu"].data_ptr(),
+            ws["din_s"].data_ptr(), self.dws.data_ptr(), None, None, None, self.e_local, total, hidden, inter, m_pad,
+            avg, 1, None, stream), "grouped_gemm (down)")
+        _lib.check(L.b200_nvfp4_ep_reduce_return_p2p(pb.peer_ret, ws["dout"].data_ptr(), ws["pos"].data_ptr(),
+                                                     ws["wts"].data_ptr(), pb.cnt.data_ptr(), self.rank, w, pb.slot_rows,
+                                                     hidden, k, stream), "ep_reduce_return_p2p")
+
+    @torch.no_grad()
+    def p2p_finish(self, ret_pos, out_bf16: bool = True):
+        """Phase 3: sum the partial rows that came back, in ascending rank order."""
+        t, w = ret_pos.shape
+        if self._ones is None or self._ones.shape != (t, w) or self._ones.device != ret_pos.device:
+            self._ones = torch.ones((t, w), dtype=torch.float32, device=ret_pos.device)
+        return self.backend.reduce(self.peers.ret, ret_pos, self._ones, out_bf16)
+
+    def _forward_p2p(self, x, topk_ids, topk_weights, out_bf16: bool):
+        ret_pos = self.p2p_dispatch(x, topk_ids, topk_weights)
+        self.peers.barrier()
+        self.p2p_compute_and_return()
+        self.peers.barrier()
+        return self.p2p_finish(ret_pos, out_bf16)
 
     @torch.no_grad()
     def forward(self, x, topk_ids, topk_weights, out_bf16: bool = True):

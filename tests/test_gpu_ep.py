@@ -82,16 +82,30 @@ def test_layer_on_one_rank_matches_oracle(backend):
     check_gemm_parity(out.cpu().numpy(), want.astype(np.float32))
 
 
-@pytest.mark.parametrize("world", [4, 8])
+class _EmulatedPeers:
+    """Slotted buffers of one emulated rank; the pointer tables address every emulated rank's buffers."""
+
+    def __init__(self, rank, world, slot_rows, hidden, topk, rec, cnt, ret):
+        import ctypes
+        arr = ctypes.c_void_p * world
+        self.slot_rows, self.hidden, self.topk = slot_rows, hidden, topk
+        self.peer_rec = arr(*[t.data_ptr() for t in rec])
+        self.peer_cnt = arr(*[t.data_ptr() for t in cnt])
+        self.peer_ret = arr(*[t.data_ptr() for t in ret])
+        self.rec, self.cnt, self.ret = rec[rank], cnt[rank], ret[rank]
+
+    def barrier(self):
+        pass
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_peer_memory_hand_off_emulated_on_one_gpu(backend, world):
-    # All ranks of the peer-memory transport on one GPU: every "rank" has its own slotted buffers,
-    # the peer pointer tables point at the other ranks' buffers on the same device, and the phases
-    # run rank after rank where the real layer has its two barriers. Checks the slot addressing of
-    # dispatch / unpack / return for more than two ranks against the oracle's per-rank composition.
-    import ctypes
-    from sm120_nvfp4_b200 import _lib, ops
-    from sm120_nvfp4_b200.ep import record_bytes
-    L = _lib.lib()
+    # All ranks of the peer-memory transport in one process on one GPU: every emulated rank has its
+    # own slotted buffers, the pointer tables address the other ranks' buffers on the same device, and
+    # the three phases of the layer run rank after rank where the real layer has its two barriers.
+    # Checks the layer code and the slot addressing of dispatch / unpack / reduce-and-return for more
+    # than two ranks against the oracle's per-rank composition, over two calls (slot reuse).
+    from sm120_nvfp4_b200.ep import ExpertParallelMoE, record_bytes
     experts, hidden, inter, topk, tokens, slot = 2 * world, 128, 64, 3, 29, 32
     e_local = experts // world
     gw = np.empty((experts, 2 * inter, hidden // 2), np.uint8)
@@ -101,47 +115,31 @@ def test_peer_memory_hand_off_emulated_on_one_gpu(backend, world):
     for e in range(experts):
         gw[e], gws[e] = randn_quantized(2 * inter, hidden, 10 + 2 * e, 0.5)
         dw[e], dws[e] = randn_quantized(hidden, inter, 11 + 2 * e, 0.5)
-    rb = record_bytes(hidden, topk)
     rows = world * slot
-    rec = [torch.zeros((rows, rb), dtype=torch.uint8, device="cuda") for _ in range(world)]
+    rec = [torch.zeros((rows, record_bytes(hidden, topk)), dtype=torch.uint8, device="cuda") for _ in range(world)]
     cnt = [torch.zeros(world, dtype=torch.int32, device="cuda") for _ in range(world)]
     ret = [torch.zeros((rows, hidden), dtype=torch.float16, device="cuda") for _ in range(world)]
-    arr = ctypes.c_void_p * world
-    peer_rec, peer_cnt, peer_ret = (arr(*[t.data_ptr() for t in ts]) for ts in (rec, cnt, ret))
-    stream = torch.cuda.current_stream().cuda_stream
-    inputs, ret_pos = [], []
-    for r in range(world):                                   # phase 1: every rank dispatches
-        x = _bf16_rows(tokens, hidden, 100 + r).cuda()
-        ids, w = topk_routing(tokens, experts, topk, 200 + r)
-        ids_t, w_t = torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()
-        dest = backend.dest_ranks(ids_t, e_local, world)
-        pos, counts, cu = backend.route(dest, world)
-        rp = torch.empty((tokens, world), dtype=torch.int32, device="cuda")
-        assert L.b200_nvfp4_ep_dispatch_p2p(peer_rec, peer_cnt, rp.data_ptr(), x.data_ptr(), ids_t.data_ptr(),
-                                            w_t.data_ptr(), pos.data_ptr(), counts.data_ptr(), cu.data_ptr(), r, world,
-                                            slot, tokens, hidden, topk, 1, stream) == 0
-        inputs.append((x, ids, w))
-        ret_pos.append(rp)
-    for r in range(world):                                   # phase 2: every rank computes and returns
-        xq = torch.empty((rows, hidden // 2), dtype=torch.uint8, device="cuda")
-        xs = torch.empty(((rows + 127) // 128 * 128) * ops.scale_k_padded(hidden), dtype=torch.uint8, device="cuda")
-        rid = torch.empty((rows, topk), dtype=torch.int32, device="cuda")
-        rw = torch.empty((rows, topk), dtype=torch.float32, device="cuda")
-        assert L.b200_nvfp4_ep_unpack_slots(xq.data_ptr(), xs.data_ptr(), rid.data_ptr(), rw.data_ptr(),
-                                            rec[r].data_ptr(), cnt[r].data_ptr(), world, slot, hidden, topk, stream) == 0
+    layers = []
+    for r in range(world):
         sl = slice(r * e_local, (r + 1) * e_local)
-        part = ops.fused_moe(xq, xs, torch.from_numpy(gw[sl].copy()).cuda(), torch.from_numpy(gws[sl].copy()).cuda(),
-                             torch.from_numpy(dw[sl].copy()).cuda(), torch.from_numpy(dws[sl].copy()).cuda(), rid, rw,
-                             ep_rank=r, num_experts=experts)
-        assert L.b200_nvfp4_ep_return_p2p(peer_ret, part.data_ptr(), cnt[r].data_ptr(), r, world, slot, hidden * 2,
-                                          stream) == 0
-    ones = torch.ones((tokens, world), dtype=torch.float32, device="cuda")
-    for r in range(world):                                   # phase 3: every rank sums its partial rows
-        out = backend.reduce(ret[r], ret_pos[r], ones, False)
-        torch.cuda.synchronize()
-        x, ids, w = inputs[r]
-        xb = x.cpu().view(torch.int16).numpy().view(np.uint16)
-        want = expected_ep_output(xb, ids, w, gw, gws, dw, dws, world).astype(np.float32)
-        got = out.cpu().numpy().astype(np.float32)
-        frob = np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)
-        assert frob < 2e-2, (r, frob)
+        peers = _EmulatedPeers(r, world, slot, hidden, topk, rec, cnt, ret)
+        layers.append(ExpertParallelMoE(*(torch.from_numpy(a[sl].copy()).cuda() for a in (gw, gws, dw, dws)), experts,
+                                        backend=backend, transport="p2p", emulate=(world, r, peers)))
+    for call in range(2):
+        inputs, ret_pos = [], []
+        for r in range(world):                               # phase 1 on every rank, then the barrier
+            x = _bf16_rows(tokens - call, hidden, 100 + r + 10 * call).cuda()
+            ids, w = topk_routing(tokens - call, experts, topk, 200 + r + 10 * call)
+            ret_pos.append(layers[r].p2p_dispatch(x, torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()))
+            inputs.append((x, ids, w))
+        for r in range(world):                               # phase 2 on every rank, then the barrier
+            layers[r].p2p_compute_and_return()
+        for r in range(world):                               # phase 3
+            out = layers[r].p2p_finish(ret_pos[r], out_bf16=False)
+            torch.cuda.synchronize()
+            x, ids, w = inputs[r]
+            xb = x.cpu().view(torch.int16).numpy().view(np.uint16)
+            want = expected_ep_output(xb, ids, w, gw, gws, dw, dws, world).astype(np.float32)
+            got = out.cpu().numpy().astype(np.float32)
+            frob = np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)
+            assert frob < 2e-2, (call, r, frob)
