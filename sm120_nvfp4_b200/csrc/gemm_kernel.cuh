@@ -261,7 +261,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   //            ~520-cycle stage.
   // empty:     the MMAs that read the stage are done
   // sf_landed: a slot of the scale ring received its atoms
-  // sf_free:   the four mover warps have read the slot into registers
+  // sf_free:   the moving team has read the slot into registers and the other team has seen it land
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* sf_landed_bar = empty_bar + kMaxStages;
   uint64_t* sf_free_bar = sf_landed_bar + kMaxSfSlots;
@@ -305,7 +305,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int s = lane; s < kSfSlots; s += 32) {
       ptx::mbar_init(sf_landed_bar + s, 1);
-      ptx::mbar_init(sf_free_bar + s, 4);
+      ptx::mbar_init(sf_free_bar + s, 4 * kSfMoverTeams);   // every mover warp, see the movers
     }
     if (lane < 2) {
       ptx::mbar_init(acc_full_bar + lane, 1);
@@ -630,6 +630,12 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // the other team it would take the older completed phase for the one it waits for (stale
         // scales, and a fifth arrival on a four-arrival `sf_free` phase).
         if (!ptx::mbar_wait(landed_a, slot_phase, abort_flag, 5)) { ok = false; break; }
+        // The reverse hazard: a warp that falls behind must still find the phase it waits for. If only
+        // the moving team released the slot, the loader could refill it (phase n + 1, a k-stage the
+        // lagging team has to move) before a lagging warp had looked at phase n; that warp would then
+        // wait for phase n + 2, which needs its own release first - a deadlock. So the slot is handed
+        // back by all mover warps: the other team's release says "seen", not "read".
+        if (!mine && ptx::elect_one()) ptx::mbar_arrive(free_a);
         if (mine) {
           // 1. atoms of this k-stage: shared memory -> registers. Every lane polls: a
           //    single-lane wait costs a vote and a broadcast per call.

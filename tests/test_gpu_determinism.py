@@ -66,3 +66,30 @@ def test_dense_gemm_is_deterministic(ops, tile_n):
     sfb = torch.randint(0x28, 0x40, (ops.scale_b_elements(m, n, k),), dtype=torch.uint8, device="cuda", generator=g)
     junk = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
     _repeat(lambda: ops.cute_gemm(a, b, sfa, sfb), 120, junk)
+
+
+def test_many_ragged_groups_finish_without_a_timed_out_wait(ops):
+    # 32 groups of about a thousand rows each, none a multiple of the tile height: every group ends
+    # in a ragged tile whose rows leave by predicated stores, which hold up the other warps' shared
+    # memory and barrier traffic for microseconds. A scale-mover warp delayed that long used to miss
+    # a phase of a slot's `landed` barrier (the slot was released by the other team alone) and wait
+    # for a phase that needed its own release: one launch in three ended in a timed-out wait.
+    from sm120_nvfp4_b200 import _lib
+    _lib.lib().b200_nvfp4_set_tile_n(0)
+    groups, n, k = 32, 4096, 7168
+    rng = np.random.default_rng(0xB2000301)
+    counts = (1024 + rng.integers(-75, 76, groups)).astype(np.int32)
+    counts += (counts % 256 == 0)
+    cu = np.zeros(groups + 1, np.int32)
+    cu[1:] = np.cumsum(counts)
+    total = int(cu[-1])
+    pad = (int(counts.max()) + 127) // 128 * 128
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randint(0, 256, (total, k // 2), dtype=torch.uint8, device="cuda", generator=g)
+    w = torch.randint(0, 256, (groups, n, k // 2), dtype=torch.uint8, device="cuda", generator=g)
+    xs = torch.randint(0x28, 0x40, (groups, pad * ops.scale_k_padded(k)), dtype=torch.uint8, device="cuda", generator=g)
+    ws = torch.randint(0x28, 0x40, (groups, n * ops.scale_k_padded(k)), dtype=torch.uint8, device="cuda", generator=g)
+    dc, dcu = torch.from_numpy(counts).cuda(), torch.from_numpy(cu).cuda()
+    junk = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _repeat(lambda: ops.grouped_gemm(x, w, dc, dcu, xs, ws), 60, junk)
+    assert _lib.device_error() == 0

@@ -340,3 +340,56 @@ def test_fused_gate_up_epilogue_matches_separate_steps(ops, counts, hidden, inte
         assert int(want.sum()) > 0
     finally:
         L.b200_nvfp4_set_tile_n(0)
+
+
+def test_row_movers_and_gathering_quantiser(ops):
+    # the building blocks for a dispatcher that ships one row per (token, expert) assignment:
+    # scatter by routing position, gather by map, and the row quantiser reading through a row map
+    from sm120_nvfp4_b200 import _lib
+    L = _lib.lib()
+    tokens, topk, experts, hidden = 50, 3, 4, 128
+    rng = np.random.default_rng(21)
+    x = torch.from_numpy(rng.standard_normal((tokens, hidden), dtype=np.float32)).to(torch.bfloat16).cuda()
+    ids, _ = topk_routing(tokens, experts, topk, 5)
+    ids_t = _dev(ids)
+    pos = torch.empty((tokens, topk), dtype=torch.int32, device="cuda")
+    seq = torch.empty(experts, dtype=torch.int32, device="cuda")
+    cu = torch.empty(experts + 1, dtype=torch.int32, device="cuda")
+    st = _stream()
+    assert L.b200_nvfp4_moe_route(ids_t.data_ptr(), pos.data_ptr(), seq.data_ptr(), cu.data_ptr(), tokens, topk, experts,
+                                  0, st) == 0
+    total = tokens * topk
+    rows = torch.zeros((total, hidden), dtype=torch.bfloat16, device="cuda")
+    assert L.b200_nvfp4_moe_scatter_rows(rows.data_ptr(), x.data_ptr(), pos.data_ptr(), total, topk, hidden * 2, st) == 0
+    p = pos.cpu().numpy().reshape(-1)
+    want_rows = np.zeros((total, hidden), np.uint16)
+    want_rows[p] = x.cpu().view(torch.int16).numpy().view(np.uint16)[np.arange(total) // topk]
+    np.testing.assert_array_equal(rows.cpu().view(torch.int16).numpy().view(np.uint16), want_rows)
+    # gather back through the inverse map
+    inv = torch.from_numpy(np.argsort(p).astype(np.int32)).cuda()       # grouped row -> flat assignment
+    back = torch.zeros_like(rows)
+    assert L.b200_nvfp4_moe_gather_rows(back.data_ptr(), rows.data_ptr(), pos.view(-1).data_ptr(), total, hidden * 2, st) == 0
+    np.testing.assert_array_equal(back.cpu().view(torch.int16).numpy().view(np.uint16),
+                                  x.cpu().view(torch.int16).numpy().view(np.uint16)[np.arange(total) // topk])
+    # quantise rows read through a map = quantise the gathered rows
+    pad = 128
+    perm = torch.from_numpy(rng.permutation(total).astype(np.int32)).cuda()
+    shuffled = torch.empty_like(rows)
+    shuffled[perm.long()] = rows                                      # shuffled[perm[i]] = rows[i]
+    got = torch.zeros((total, hidden // 2), dtype=torch.uint8, device="cuda")
+    got_s = torch.zeros((experts, pad * ops.scale_k_padded(hidden)), dtype=torch.uint8, device="cuda")
+    assert L.b200_nvfp4_moe_quantize_expert_gather(got.data_ptr(), got_s.data_ptr(), shuffled.data_ptr(), perm.data_ptr(),
+                                                   seq.data_ptr(), cu.data_ptr(), experts, total, hidden, pad, 1, 1, st) == 0
+    want, want_s = ops.quantize_expert(rows, seq, cu, scale_m_pad=pad)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    nkb = hidden // 16
+    counts = seq.cpu().numpy()
+    for e in range(experts):
+        if counts[e] == 0:
+            continue
+        r = np.repeat(np.arange(int(counts[e]), dtype=np.int32), nkb)
+        kb = np.tile(np.arange(nkb, dtype=np.int32), int(counts[e]))
+        off = oracle.sf_offsets(r, kb, hidden)
+        np.testing.assert_array_equal(got_s[e].cpu().numpy()[off], want_s[e].cpu().numpy()[off])
+    assert inv.numel() == total
