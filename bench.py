@@ -503,6 +503,18 @@ def main():
         line = run_moe(args, world, rank, device, peaks)
     else:
         line = run_gemm(args, world, rank, device, peaks)
+    # A bounded wait inside a kernel that gave up makes the launch finish (late) with wrong results:
+    # a number measured over such a launch is not a measurement.
+    from sm120_nvfp4_b200 import _lib
+    err = _lib.device_error()
+    if world > 1:
+        import torch.distributed as dist
+        worst = torch.tensor([err], dtype=torch.int64, device=device)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        err = int(worst.item())
+    if err:
+        raise SystemExit(f"a kernel reported a timed-out wait (device error word {err}: code {err & 255}, "
+                         f"block {err >> 8}); no result printed")
     if rank == 0 and world == 1 and args.workload != "moe":
         tf, dt, cores = cpu_gemm_sample(line["config"]["m"], line["config"]["n"], line["config"]["k"], 4096, 8192)
         line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
