@@ -68,14 +68,15 @@ def test_dense_gemm_is_deterministic(ops, tile_n):
     _repeat(lambda: ops.cute_gemm(a, b, sfa, sfb), 120, junk)
 
 
-def test_many_ragged_groups_finish_without_a_timed_out_wait(ops):
+@pytest.mark.parametrize("tile_n", [0, 128, 256])
+def test_many_ragged_groups_finish_without_a_timed_out_wait(ops, tile_n):
     # 32 groups of about a thousand rows each, none a multiple of the tile height: every group ends
     # in a ragged tile whose rows leave by predicated stores, which hold up the other warps' shared
     # memory and barrier traffic for microseconds. A scale-mover warp delayed that long used to miss
     # a phase of a slot's `landed` barrier (the slot was released by the other team alone) and wait
     # for a phase that needed its own release: one launch in three ended in a timed-out wait.
     from sm120_nvfp4_b200 import _lib
-    _lib.lib().b200_nvfp4_set_tile_n(0)
+    _lib.lib().b200_nvfp4_set_tile_n(tile_n)
     groups, n, k = 32, 4096, 7168
     rng = np.random.default_rng(0xB2000301)
     counts = (1024 + rng.integers(-75, 76, groups)).astype(np.int32)
