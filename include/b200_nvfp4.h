@@ -99,6 +99,26 @@ B200_NVFP4_API int b200_nvfp4_gemm_splitk_static(int m, int n, int k, int split_
                                                  const void* b, const void* sfa, const void* sfb,
                                                  void* c_f16, b200_stream_t stream);
 
+/* GEMM on operands in host memory, C_host = A_host x B_host^T (FP16), with the copies in both
+ * directions overlapped with the arithmetic: A and B are uploaded in chunks of block_rows /
+ * block_cols rows (alternately), the block of C that a pair of chunks completes is computed as
+ * soon as both have landed and copied home while later chunks still arrive. No counterpart in
+ * the reference, whose entry points take device pointers only; it serves callers whose data
+ * starts and ends on the host, for whom the copies, not the kernel, are the cost.
+ *   - *_host: the same layouts as b200_nvfp4_gemm's operands, in host memory (page-locked
+ *     memory lets the copies run asynchronously and overlap);
+ *   - *_dev: device scratch of the same sizes (A m*k/2, B n*k/2, the two scale regions,
+ *     C m*n*2 bytes); the library allocates none. C's scratch holds blocks, not a matrix.
+ *   - block_rows, block_cols: multiples of 128, 0 for the defaults (1024, 2048); at most 64
+ *     chunks per operand;
+ *   - everything is enqueued; `stream` waits for the last copy, so synchronising `stream`
+ *     is enough before reading c_host_f16. Calls on one device are serialised on the host. */
+B200_NVFP4_API int b200_nvfp4_gemm_host(int m, int n, int k, const void* a_host, const void* b_host,
+                                        const void* sfa_host, const void* sfb_host, void* c_host_f16,
+                                        void* a_dev, void* b_dev, void* sfa_dev, void* sfb_dev,
+                                        void* c_dev, int block_rows, int block_cols,
+                                        b200_stream_t stream);
+
 /* nvfp4_gemm_sm120 (src/gemm/gemm_dispatch.cu:63-90): default dispatcher. */
 B200_NVFP4_API int b200_nvfp4_gemm_auto(int m, int n, int k, const void* a, const void* b,
                                         const void* sfa, const void* sfb, void* c_f16,

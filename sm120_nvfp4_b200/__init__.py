@@ -11,7 +11,7 @@ include/b200_nvfp4.h on torch's current stream. torch is used for memory and str
 """
 from __future__ import annotations
 
-from .ops import (cute_gemm, cutlass_gemm, expert_moe, expert_moe_workspace_bytes, fused_moe, gemm,
+from .ops import (HostGemm, cute_gemm, cutlass_gemm, expert_moe, expert_moe_workspace_bytes, fused_moe, gemm,
                   grouped_gemm, pack_weights, quantize_expert, router_topk, scale_a_elements, scale_b_elements,
                   scale_k_padded)
 
@@ -30,4 +30,6 @@ __all__ = [
     # not in the reference package: the callers either side of the routed layer
     "router_topk",
     "pack_weights",
+    # host-memory operands, copies overlapped with the arithmetic
+    "HostGemm",
 ]

@@ -30,6 +30,7 @@ _SIGNATURES = {
     "b200_nvfp4_gemm_splitk": (ci, [ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, C.c_size_t, vp]),
     "b200_nvfp4_gemm_splitk_static_max_elements": (C.c_size_t, []),
     "b200_nvfp4_gemm_splitk_static": (ci, [ci, ci, ci, ci, vp, vp, vp, vp, vp, vp]),
+    "b200_nvfp4_gemm_host": (ci, [ci, ci, ci] + [vp] * 10 + [ci, ci, vp]),
     "b200_nvfp4_gemm_auto": (ci, [ci, ci, ci, vp, vp, vp, vp, vp, vp, C.c_size_t, vp]),
     "b200_nvfp4_grouped_gemm": (ci, [vp] * 10 + [ci] * 7 + [vp, vp]),
     "b200_nvfp4_moe_count_and_gather": (ci, [vp] * 8 + [ci] * 8 + [vp]),

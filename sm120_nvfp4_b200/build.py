@@ -19,7 +19,7 @@ PKG = Path(__file__).resolve().parent
 ROOT = PKG.parent
 CSRC = PKG / "csrc"
 OUT = PKG / "libb200_nvfp4.so"
-SOURCES = ["gemm.cu", "gemm_splitk_static.cu", "moe_kernels.cu", "ep_kernels.cu", "fused_moe.cu", "host_common.cpp", "api.cpp"]
+SOURCES = ["gemm.cu", "gemm_splitk_static.cu", "gemm_host.cu", "moe_kernels.cu", "ep_kernels.cu", "fused_moe.cu", "host_common.cpp", "api.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-Xptxas", "-v",
               f"-I{ROOT / 'include'}", f"-I{CSRC}"]

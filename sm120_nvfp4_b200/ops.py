@@ -106,6 +106,49 @@ def cutlass_gemm(a: torch.Tensor, b: torch.Tensor, sfa: torch.Tensor, sfb: torch
     return _gemm_common(a, b, sfa, sfb, "generic")
 
 
+class HostGemm:
+    """GEMM on operands that live in (page-locked) host memory: `run(a, b, sfa, sfb, out)` uploads A and B
+    in chunks, computes each block of C as soon as its two chunks have landed and copies it home while
+    later chunks still arrive (`b200_nvfp4_gemm_host`). The object owns the device scratch for one
+    problem size; the result is complete once the current stream has been synchronised. Not in the
+    reference, whose operators take device tensors only."""
+
+    def __init__(self, m: int, n: int, k: int, device=None, block_rows: int = 0, block_cols: int = 0):
+        _check(m > 0 and n > 0 and k > 0 and k % 32 == 0 and n % 8 == 0,
+               "M, N, K must be positive, K % 32 == 0 and N % 8 == 0")
+        self.m, self.n, self.k = m, n, k
+        self.block_rows, self.block_cols = block_rows, block_cols
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        u8 = dict(dtype=torch.uint8, device=self.device)
+        self._a = torch.empty((m, k // 2), **u8)
+        self._b = torch.empty((n, k // 2), **u8)
+        self._sfa = torch.empty(scale_a_elements(m, n, k), **u8)
+        self._sfb = torch.empty(scale_b_elements(m, n, k), **u8)
+        self._c = torch.empty((m, n), dtype=torch.float16, device=self.device)
+
+    def run(self, a: torch.Tensor, b: torch.Tensor, sfa: torch.Tensor, sfb: torch.Tensor,
+            out: torch.Tensor = None) -> torch.Tensor:
+        m, n, k = self.m, self.n, self.k
+        for t, name in ((a, "a"), (b, "b"), (sfa, "sfa"), (sfb, "sfb")):
+            _check(not t.is_cuda and t.is_contiguous(), f"{name} must be a contiguous host tensor")
+        _check(_is_packed(a) and _is_packed(b) and tuple(a.shape) == (m, k // 2) and tuple(b.shape) == (n, k // 2),
+               "a must be packed [M, K/2] and b packed [N, K/2]")
+        _check(sfa.dtype == torch.uint8 and sfb.dtype == torch.uint8 and sfa.numel() == self._sfa.numel()
+               and sfb.numel() == self._sfb.numel(), "sfa / sfb have the wrong dtype or physical size")
+        if out is None:
+            out = torch.empty((m, n), dtype=torch.float16).pin_memory()
+        _check(not out.is_cuda and out.is_contiguous() and out.dtype == torch.float16 and tuple(out.shape) == (m, n),
+               "out must be a contiguous float16 host tensor [M, N]")
+        L = _lib.lib()
+        with torch.cuda.device(self.device):
+            status = L.b200_nvfp4_gemm_host(m, n, k, a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
+                                            out.data_ptr(), self._a.data_ptr(), self._b.data_ptr(),
+                                            self._sfa.data_ptr(), self._sfb.data_ptr(), self._c.data_ptr(),
+                                            self.block_rows, self.block_cols, _stream(self.device))
+        _check(status == 0, f"NVFP4 host GEMM failed: {_lib.status_string(status)}")
+        return out
+
+
 # ------------------------------------------------------------------- grouped GEMM
 
 

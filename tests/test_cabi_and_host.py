@@ -69,7 +69,7 @@ def test_python_surface_mirrors_reference_names():
     import torch
     for name in ("gemm", "cute_gemm", "cutlass_gemm", "grouped_gemm", "fused_moe", "quantize_expert",
                  "expert_moe", "expert_moe_workspace_bytes", "scale_k_padded", "scale_a_elements",
-                 "scale_b_elements", "router_topk", "pack_weights"):
+                 "scale_b_elements", "router_topk", "pack_weights", "HostGemm"):
         assert callable(getattr(pkg, name))
     for op in ("gemm", "cute_gemm", "cutlass_gemm", "grouped_gemm", "fused_moe", "quantize_expert", "expert_moe"):
         assert hasattr(torch.ops.sm120_nvfp4, op)
