@@ -109,7 +109,7 @@ B200_NVFP4_API int b200_nvfp4_gemm_splitk_static(int m, int n, int k, int split_
  *     memory lets the copies run asynchronously and overlap);
  *   - *_dev: device scratch of the same sizes (A m*k/2, B n*k/2, the two scale regions,
  *     C m*n*2 bytes); the library allocates none. C's scratch holds blocks, not a matrix.
- *   - block_rows, block_cols: multiples of 128, 0 for the defaults (1024, 2048); at most 64
+ *   - block_rows, block_cols: multiples of 128, 0 for the defaults (2048, 2048); at most 64
  *     chunks per operand;
  *   - everything is enqueued; `stream` waits for the last copy, so synchronising `stream`
  *     is enough before reading c_host_f16. Calls on one device are serialised on the host. */

@@ -74,7 +74,7 @@ int b200_nvfp4_gemm_host(int m, int n, int k, const void* a_host, const void* b_
   if (!a_host || !b_host || !sfa_host || !sfb_host || !c_host_f16 || !a_dev || !b_dev || !sfa_dev ||
       !sfb_dev || !c_dev)
     return B200_NVFP4_INVALID_ARGUMENT;
-  if (block_rows == 0) block_rows = 1024;
+  if (block_rows == 0) block_rows = 2048;
   if (block_cols == 0) block_cols = 2048;
   // chunks start on scale-atom boundaries (128 rows), so a chunk's scales are one contiguous range
   if (block_rows < 128 || block_cols < 128 || (block_rows % 128) != 0 || (block_cols % 128) != 0)

@@ -61,6 +61,10 @@ def test_argument_validation_without_gpu():
     assert L.b200_nvfp4_gemm_auto(128, 4096, 8192, 16, 16, 16, 16, 16, None, 0, None) == 3
     assert L.b200_nvfp4_gemm_auto(128, 4096, 8192, 16, 16, 16, 16, 16, 16, 100, None) == 3
     assert L.b200_nvfp4_expert_moe(16, 16, 16, 16, 16, 16, 16, 16, 16, None, 0, 5, 128, 64, 2, 128, None) == 3
+    # host-memory GEMM: chunk sizes must be multiples of the 128-row scale atoms; no null pointers
+    assert L.b200_nvfp4_gemm_host(256, 256, 128, *([16] * 10), 100, 128, None) == 1
+    assert L.b200_nvfp4_gemm_host(256, 256, 128, *([16] * 9), None, 128, 128, None) == 1
+    assert L.b200_nvfp4_gemm_host(256, 260, 128, *([16] * 10), 128, 128, None) == 1
     assert L.b200_nvfp4_set_tile_n(48) == 1 and L.b200_nvfp4_set_tile_n(32) == 1 and L.b200_nvfp4_set_tile_n(0) == 0
 
 
