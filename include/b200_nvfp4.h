@@ -325,6 +325,19 @@ B200_NVFP4_API int b200_nvfp4_ep_unpack_slots(void* x_packed, void* x_scale, voi
 B200_NVFP4_API int b200_nvfp4_ep_return_p2p(const void* const* peer_ret, const void* partial,
                                             const void* counts, int my_rank, int world,
                                             int slot_rows, int row_bytes, b200_stream_t stream);
+/* Cross-GPU barrier between the phases of the peer-memory hand-off (no counterpart in the
+ * reference, whose hand-off script synchronises through the collective library,
+ * benchmarks/integration/benchmark_deepep_handoff.py:466-496). peer_flags[r] points at rank r's
+ * `world` int32 flag words (zero before the first call); `epoch` is 1, 2, 3, ... over the calls of
+ * one flag set, the same on every rank. The kernel publishes the epoch in flag `my_rank` of every
+ * rank (after a system-scope fence) and waits until all of its own flags have reached it. The wait
+ * is bounded: after limit_cycles SM clocks (0 = about one second) it stores 9 | (late rank << 8) in
+ * the device error word (b200_nvfp4_device_error) and returns; what follows on the stream then
+ * runs on incomplete data, which the error word tells. Ranks must be separate GPUs: two launches
+ * that wait for each other on one GPU may never run at the same time. */
+B200_NVFP4_API int b200_nvfp4_ep_barrier_p2p(const void* const* peer_flags, int my_rank, int world,
+                                             int epoch, long long limit_cycles, b200_stream_t stream);
+
 /* ep_return_p2p fused with the reduce step that produces `partial`: the weighted sum over a slot
  * row's local experts (b200_nvfp4_moe_reduce arithmetic, FP16 result, no shared-expert term) is
  * stored straight into the source rank's return slot. down_output / topk_pos / topk_scale are the

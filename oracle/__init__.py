@@ -59,6 +59,8 @@ def lib():
         L.oracle_gemm_workspace_size.restype = C.c_uint64
         L.oracle_gemm_workspace_size.argtypes = [C.c_int] * 3
         L.oracle_num_threads.restype = C.c_int
+        L.oracle_set_num_threads.restype = None
+        L.oracle_set_num_threads.argtypes = [C.c_int]
         for name in ("oracle_quantize_rows_f32", "oracle_gemm_sampled", "oracle_gemm",
                      "oracle_grouped_gemm", "oracle_splitk_reduce", "oracle_count_and_gather",
                      "oracle_act_mul_and_quant", "oracle_quantize_expert", "oracle_reduce",
@@ -91,6 +93,13 @@ def ref():
             getattr(R, n).argtypes = [C.c_uint8]
         _ref = R
     return _ref
+
+
+def set_threads(n: int) -> int:
+    """Use n OpenMP threads from now on (e.g. all host cores under a launcher that exported
+    OMP_NUM_THREADS=1); returns the count in effect."""
+    lib().oracle_set_num_threads(int(n))
+    return int(lib().oracle_num_threads())
 
 
 def _p(a, t):

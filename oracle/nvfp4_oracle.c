@@ -12,7 +12,7 @@
  * the scale-offset formula of tests/python/test_fused_moe.py:160-168) and the
  * CUTLASS / CUDA-toolkit host conversions the reference calls
  * (cutlass::float_ue4m3_t, cutlass::float_e2m1_t, __nv_cvt_float_to_fp4),
- * compiled from their own headers by oracle/build_ref.py into oracle/_ref/.
+ * compiled from their own headers by oracle/build.py into oracle/_ref/.
  * The accumulation order inside the reference's tensor-core MMA is not pinned
  * by any reference test ("parity unpinned" for that detail only): every
  * reference test uses exactly representable sums, so the GEMM oracle computes
@@ -665,5 +665,15 @@ ORACLE_API int oracle_num_threads(void) {
   return omp_get_max_threads();
 #else
   return 1;
+#endif
+}
+
+/* Thread count of the next parallel loops. A launcher that pins OMP_NUM_THREADS=1 for its
+ * worker processes (torchrun does) would otherwise make the timed CPU baseline single-threaded. */
+ORACLE_API void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
 #endif
 }

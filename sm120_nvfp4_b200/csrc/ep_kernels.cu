@@ -350,11 +350,41 @@ ep_reduce_return_p2p_kernel(PeerPointers peer_ret, const __half* __restrict__ do
   }
 }
 
-bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+// Cross-GPU barrier of the peer-memory transport. Every rank owns `world` flag words in its
+// symmetric buffer; flag s of rank r is written by rank s only. Thread r of the one block stores
+// this call's epoch into flag `my_rank` of rank r (after a system-scope fence, so the peer stores
+// of the kernels before it on the stream are visible first), then waits until its own flag r has
+// reached the epoch. The wait is bounded: after `limit_cycles` it records
+// kBarrierTimeoutCode | (late rank << 8) in the device error word and returns, so a rank that
+// is late, failed or gone costs the others one time-out instead of an endless spin. Epochs only
+// grow (signed difference compare, so the counter may wrap).
+constexpr int kBarrierTimeoutCode = 9;
 
-int check_launch() {
-  return cudaPeekAtLastError() == cudaSuccess ? B200_NVFP4_SUCCESS : B200_NVFP4_CUDA_ERROR;
+__global__ void __launch_bounds__(kMaxWorld)
+ep_barrier_kernel(PeerPointers peer_flags, int my_rank, int world, int epoch, long long limit_cycles,
+                  int* __restrict__ error) {
+  const int r = threadIdx.x;
+  if (r < world) {
+    __threadfence_system();
+    int* remote = reinterpret_cast<int*>(peer_flags.p[r]) + my_rank;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+    const int* local = reinterpret_cast<const int*>(peer_flags.p[my_rank]) + r;
+    const long long start = clock64();
+    while (true) {
+      int seen;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(local) : "memory");
+      if (seen - epoch >= 0) break;
+      if (clock64() - start > limit_cycles) {
+        if (error != nullptr) atomicCAS(error, 0, kBarrierTimeoutCode | (r << 8));
+        break;
+      }
+      __nanosleep(64);
+    }
+    __threadfence_system();
+  }
 }
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
 }  // namespace b200
@@ -376,7 +406,7 @@ int b200_nvfp4_ep_dest_ranks(const void* topk_ids, void* dest, int num_tokens, i
       static_cast<const int*>(topk_ids), static_cast<int*>(dest), num_tokens, num_topk,
       experts_per_rank, world);
   b200::count_launch();
-  return b200::check_launch();
+  return b200::launch_status();
 }
 
 int b200_nvfp4_ep_pack_rows(void* records, const void* x, const void* topk_ids,
@@ -408,7 +438,7 @@ int b200_nvfp4_ep_pack_rows(void* records, const void* x, const void* topk_ids,
                                                                         hidden_size, num_topk, world);
   }
   b200::count_launch();
-  return b200::check_launch();
+  return b200::launch_status();
 }
 
 int b200_nvfp4_ep_unpack_rows(void* x_packed, void* x_scale, void* topk_ids, void* topk_weights,
@@ -430,7 +460,7 @@ int b200_nvfp4_ep_unpack_rows(void* x_packed, void* x_scale, void* topk_ids, voi
       static_cast<float*>(topk_weights), static_cast<const uint8_t*>(records), rows, hidden_size,
       num_topk);
   b200::count_launch();
-  return b200::check_launch();
+  return b200::launch_status();
 }
 
 int b200_nvfp4_ep_dispatch_p2p(const void* const* peer_records, const void* const* peer_counts, void* ret_pos,
@@ -473,7 +503,7 @@ int b200_nvfp4_ep_dispatch_p2p(const void* const* peer_records, const void* cons
         num_tokens, hidden_size, num_topk);
   }
   b200::count_launch();
-  return b200::check_launch();
+  return b200::launch_status();
 }
 
 int b200_nvfp4_ep_unpack_slots(void* x_packed, void* x_scale, void* topk_ids, void* topk_weights,
@@ -495,7 +525,7 @@ int b200_nvfp4_ep_unpack_slots(void* x_packed, void* x_scale, void* topk_ids, vo
       static_cast<float*>(topk_weights), static_cast<const uint8_t*>(records), static_cast<const int*>(counts),
       world, slot_rows, hidden_size, num_topk);
   b200::count_launch();
-  return b200::check_launch();
+  return b200::launch_status();
 }
 
 int b200_nvfp4_ep_return_p2p(const void* const* peer_ret, const void* partial, const void* counts, int my_rank,
@@ -519,7 +549,7 @@ int b200_nvfp4_ep_return_p2p(const void* const* peer_ret, const void* partial, c
       ret, static_cast<const uint8_t*>(partial), static_cast<const int*>(counts), my_rank, world, slot_rows,
       row_bytes);
   b200::count_launch();
-  return b200::check_launch();
+  return b200::launch_status();
 }
 
 int b200_nvfp4_ep_reduce_return_p2p(const void* const* peer_ret, const void* down_output, const void* topk_pos,
@@ -547,7 +577,28 @@ int b200_nvfp4_ep_reduce_return_p2p(const void* const* peer_ret, const void* dow
       static_cast<const float*>(topk_scale), static_cast<const int*>(counts), my_rank, world, slot_rows,
       hidden_size, num_topk);
   b200::count_launch();
-  return b200::check_launch();
+  return b200::launch_status();
+}
+
+int b200_nvfp4_ep_barrier_p2p(const void* const* peer_flags, int my_rank, int world, int epoch,
+                              long long limit_cycles, b200_stream_t stream) {
+  if (peer_flags == nullptr || world <= 0 || world > b200::kMaxWorld || my_rank < 0 || my_rank >= world ||
+      limit_cycles < 0) {
+    return B200_NVFP4_INVALID_ARGUMENT;
+  }
+  b200::PeerPointers flags{};
+  for (int r = 0; r < world; ++r) {
+    if (peer_flags[r] == nullptr || (reinterpret_cast<uintptr_t>(peer_flags[r]) & 3u) != 0)
+      return B200_NVFP4_INVALID_ARGUMENT;
+    flags.p[r] = static_cast<uint8_t*>(const_cast<void*>(peer_flags[r]));
+  }
+  int* error = b200::device_error_word();
+  if (error == nullptr) return B200_NVFP4_CUDA_ERROR;
+  const long long limit = limit_cycles > 0 ? limit_cycles : (1ll << 31);   // about a second
+  b200::ep_barrier_kernel<<<1, b200::kMaxWorld, 0, static_cast<cudaStream_t>(stream)>>>(flags, my_rank, world, epoch,
+                                                                                     limit, error);
+  b200::count_launch();
+  return b200::launch_status();
 }
 
 }  // extern "C"

@@ -187,8 +187,8 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   config.numAttrs = 1;
   const cudaError_t launched = cudaLaunchKernelEx(&config, kernel, tmap_a, tmap_b, tmap_out, p);
   count_launch();
-  return launched == cudaSuccess && cudaPeekAtLastError() == cudaSuccess ? B200_NVFP4_SUCCESS
-                                                                          : B200_NVFP4_CUDA_ERROR;
+  const int status = launch_status();
+  return launched == cudaSuccess ? status : B200_NVFP4_CUDA_ERROR;
 }
 
 // Tile shape. expected_m_tiles counts 128-row tiles.
@@ -315,8 +315,10 @@ int gemm_splitk(int m, int n, int k, int split_k, const void* a, const void* b, 
       !aligned16(sfa) || !aligned16(sfb) || !aligned16(c_f16)) {
     return B200_NVFP4_INVALID_ARGUMENT;
   }
-  const size_t required = static_cast<size_t>(split_k) * m * n * sizeof(float);
-  if (workspace_bytes < required) return B200_NVFP4_INSUFFICIENT_WORKSPACE;
+  // split_k <= ceil(K / 128) < 2^24 was checked above; M * N < 2^62, so the byte count is compared by
+  // division instead of being formed (it could exceed 64 bits)
+  const size_t slice_bytes = static_cast<size_t>(m) * static_cast<size_t>(n) * sizeof(float);
+  if (workspace_bytes / slice_bytes < static_cast<size_t>(split_k)) return B200_NVFP4_INSUFFICIENT_WORKSPACE;
   const int skp = scale_k_padded(k);
   LaunchSpec s{};
   s.num_groups = 1;
@@ -349,7 +351,7 @@ int gemm_splitk(int m, int n, int k, int split_k, const void* a, const void* b, 
       static_cast<const float*>(workspace), static_cast<__half*>(c_f16), numel8,
       static_cast<long long>(m) * n, split_k);
   count_launch();
-  return cudaPeekAtLastError() == cudaSuccess ? B200_NVFP4_SUCCESS : B200_NVFP4_CUDA_ERROR;
+  return launch_status();
 }
 
 int gemm_grouped(void* y, const void* x, const void* w, const void* seqlens,

@@ -62,11 +62,15 @@ size_t b200_nvfp4_gemm_splitk_static_max_elements(void) { return b200::kScratchF
 int b200_nvfp4_gemm_splitk_static(int m, int n, int k, int split_k, const void* a, const void* b,
                                   const void* sfa, const void* sfb, void* c_f16,
                                   b200_stream_t stream) {
-  if (m <= 0 || n <= 0 || k <= 0 || split_k < 1) return B200_NVFP4_INVALID_ARGUMENT;
-  const unsigned long long need =
-      static_cast<unsigned long long>(split_k) * static_cast<unsigned long long>(m) *
-      static_cast<unsigned long long>(n);
-  if (need > b200::kScratchFloats) return B200_NVFP4_INSUFFICIENT_WORKSPACE;
+  // split_k is bounded first (a 128-wide k-tile per split at least), so that the element count
+  // below is a product of bounded factors; each multiplication is checked against the limit by
+  // division before it is made (cf. the reference's workspace arithmetic,
+  // src/gemm/specialized/m128_gemm.cu:403-414), so huge M or N cannot wrap around into range.
+  if (m <= 0 || n <= 0 || k <= 0 || split_k < 1 || split_k > (k + 127) / 128) return B200_NVFP4_INVALID_ARGUMENT;
+  const size_t per_row = b200::kScratchFloats / static_cast<size_t>(n);        // floats of scratch per output row
+  if (per_row == 0 || static_cast<size_t>(m) > per_row) return B200_NVFP4_INSUFFICIENT_WORKSPACE;
+  const size_t slice = static_cast<size_t>(m) * static_cast<size_t>(n);        // <= kScratchFloats
+  if (static_cast<size_t>(split_k) > b200::kScratchFloats / slice) return B200_NVFP4_INSUFFICIENT_WORKSPACE;
   float* scratch = b200::splitk_scratch_for_current_device();
   if (scratch == nullptr) return B200_NVFP4_CUDA_ERROR;
   return b200::gemm_splitk(m, n, k, split_k, a, b, sfa, sfb, c_f16, scratch,

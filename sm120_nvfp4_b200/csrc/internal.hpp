@@ -12,6 +12,11 @@ extern std::atomic<long long> g_launch_count;
 
 inline void count_launch(int n = 1) { g_launch_count.fetch_add(n, std::memory_order_relaxed); }
 
+// Status of the launch(es) just issued. cudaGetLastError, not cudaPeekAtLastError: a launch that
+// was refused (bad configuration) is reported by the call that caused it and does not linger to
+// fail the next, unrelated call.
+inline int launch_status() { return cudaGetLastError() == cudaSuccess ? 0 : 6; }
+
 int gemm_dense(int groups, int m, int n, int k, const void* a, const void* b, const void* sfa,
                const void* sfb, void* c, bool out_f32, cudaStream_t stream);
 

@@ -2,6 +2,7 @@
 // rank), gather to expert-major order, SiLU*up + NVFP4 quantisation, row quantisation and
 // the weighted top-k combine. All global accesses on the payload paths are 16-byte vectors.
 #include <cstdint>
+#include <mutex>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -458,10 +459,6 @@ move_rows_kernel(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src,
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-int check_launch() {
-  return cudaPeekAtLastError() == cudaSuccess ? B200_NVFP4_SUCCESS : B200_NVFP4_CUDA_ERROR;
-}
-
 }  // namespace
 
 int moe_count_and_gather(void* gate_up_input, void* gate_up_input_scale, const void* input,
@@ -506,7 +503,7 @@ int moe_count_and_gather(void* gate_up_input, void* gate_up_input_scale, const v
                                                                 start_expert, num_expert_local);
     count_launch(3);
   }
-  if (check_launch() != B200_NVFP4_SUCCESS) return B200_NVFP4_CUDA_ERROR;
+  if (launch_status() != B200_NVFP4_SUCCESS) return B200_NVFP4_CUDA_ERROR;
   int blocks = (total + 7) / 8;
   const int max_blocks = dev.sm_count * 8;
   if (blocks > max_blocks) blocks = max_blocks;
@@ -515,7 +512,7 @@ int moe_count_and_gather(void* gate_up_input, void* gate_up_input_scale, const v
       static_cast<const uint8_t*>(input), static_cast<const uint8_t*>(input_scale), ids, pos, cu,
       total, hidden_size, num_topk, start_expert, group_stride);
   count_launch();
-  return check_launch();
+  return launch_status();
 }
 
 template <int kMode>
@@ -550,7 +547,7 @@ int launch_quant(void* output, void* output_scale, const void* input, const void
       static_cast<const int*>(seqlens), static_cast<const int*>(cu_seqlens),
       static_cast<const int*>(row_map), num_expert_local, width, group_stride);
   count_launch();
-  return check_launch();
+  return launch_status();
 }
 
 int moe_act_mul_and_quant(void* output, void* output_scale, const void* gate_up, const void* seqlens,
@@ -603,7 +600,7 @@ int moe_route(const void* topk_ids, void* topk_pos, void* seqlens, void* cu_seql
                                                                 start_expert, num_expert_local);
     count_launch(3);
   }
-  return check_launch();
+  return launch_status();
 }
 
 // Row movers of the expert-parallel driver (16-byte vectors, one warp per row).
@@ -624,7 +621,7 @@ int moe_move_rows(void* dst, const void* src, const void* index, int count, int 
                                                static_cast<const int*>(index), count, fanout, row_bytes,
                                                scatter);
   count_launch();
-  return check_launch();
+  return launch_status();
 }
 
 int moe_router_topk(const void* logits, void* topk_ids, void* topk_weights, int num_tokens,
@@ -635,6 +632,17 @@ int moe_router_topk(const void* logits, void* topk_ids, void* topk_weights, int 
   }
   const DeviceInfo& dev = current_device_info();
   if (!dev.ok) return B200_NVFP4_CUDA_ERROR;
+  // eight warps per block keep one score row each in shared memory: 128 KiB at the 4096-expert
+  // limit, which needs the opt-in above the 48 KiB default (once per device)
+  constexpr size_t kMaxRouterSmem = static_cast<size_t>(8) * 4096 * sizeof(float);
+  static std::once_flag once[64];
+  static cudaError_t attr_status[64];
+  if (dev.device < 0 || dev.device >= 64) return B200_NVFP4_CUDA_ERROR;
+  std::call_once(once[dev.device], [&] {
+    attr_status[dev.device] = cudaFuncSetAttribute(router_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   static_cast<int>(kMaxRouterSmem));
+  });
+  if (attr_status[dev.device] != cudaSuccess) return B200_NVFP4_CUDA_ERROR;
   int blocks = (num_tokens + 7) / 8;
   const int max_blocks = dev.sm_count * 8;
   if (blocks > max_blocks) blocks = max_blocks;
@@ -642,7 +650,7 @@ int moe_router_topk(const void* logits, void* topk_ids, void* topk_weights, int 
       static_cast<const float*>(logits), static_cast<int*>(topk_ids), static_cast<float*>(topk_weights),
       num_tokens, num_experts, num_topk);
   count_launch();
-  return check_launch();
+  return launch_status();
 }
 
 int moe_reduce(void* output, const void* down_output, const void* topk_pos, const void* topk_scale,
@@ -671,7 +679,7 @@ int moe_reduce(void* output, const void* down_output, const void* topk_pos, cons
         hidden_size, num_topk);
   }
   count_launch();
-  return check_launch();
+  return launch_status();
 }
 
 }  // namespace b200

@@ -24,9 +24,12 @@ kernels read and write local HBM only.
 Two transports carry the records and the partial rows. "nccl": `all_to_all_single` (one host
 read-back of the split sizes per call, as in the reference script). "p2p": no collective library
 and no host read-back in the data path - every rank owns slotted receive / return buffers in
-symmetric memory (torch.distributed._symmetric_memory, CUDA IPC over NVLink) and the pack /
+symmetric memory (torch.distributed._symmetric_memory maps them, CUDA IPC over NVLink) and the pack /
 return kernels store straight into the peer's slots (b200_nvfp4_ep_dispatch_p2p / _ep_unpack_slots
-/ _ep_return_p2p), separated by two cross-GPU barriers per layer.
+/ _ep_reduce_return_p2p), separated by two cross-GPU barriers per layer. The barrier is this
+library's kernel (b200_nvfp4_ep_barrier_p2p): epoch flags stored into the peers, a bounded wait on
+the local ones; a rank that never arrives costs the others one time-out (about a second by
+default) and shows in the device error word (_lib.device_error()), it cannot hang them.
 
 The compute steps go through a small backend object so that the host logic (splits, ordering,
 the two exchanges) can be exercised on CPU ranks with a checker backend supplied by the tests;
@@ -115,32 +118,46 @@ class CudaBackend:
 
 
 class _PeerBuffers:
-    """Slotted receive / return buffers of one rank, visible to every peer (symmetric memory)."""
+    """Slotted receive / return buffers of one rank, visible to every peer (symmetric memory), and
+    the flag words of this library's own cross-GPU barrier (b200_nvfp4_ep_barrier_p2p: peer stores
+    of an epoch, a bounded wait on the local flags, a time-out reported through the device error
+    word). torch's symmetric memory only maps the buffers; no library barrier runs per layer."""
 
-    def __init__(self, group, world: int, slot_rows: int, hidden: int, topk: int, device):
+    def __init__(self, group, world: int, slot_rows: int, hidden: int, topk: int, device, my_rank: int,
+                 barrier_limit_cycles: int = 0):
         import torch.distributed._symmetric_memory as symm_mem
         self.world, self.slot_rows, self.hidden, self.topk = world, slot_rows, hidden, topk
+        self.my_rank, self.limit = my_rank, int(barrier_limit_cycles)
         self.rb = record_bytes(hidden, topk)
         rows = world * slot_rows
         rec_bytes = rows * self.rb
         self.cnt_off = (rec_bytes + 255) // 256 * 256
-        self.ret_off = self.cnt_off + 256
+        self.flag_off = self.cnt_off + 256
+        self.ret_off = self.flag_off + 256
         total = self.ret_off + rows * hidden * 2
         self.buf = symm_mem.empty(total, dtype=torch.uint8, device=device)
-        self.handle = symm_mem.rendezvous(self.buf, group=group if group is not None else dist.group.WORLD)
+        group = group if group is not None else dist.group.WORLD
+        self.handle = symm_mem.rendezvous(self.buf, group=group)
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
         arr = ctypes.c_void_p * world
         self.peer_rec = arr(*ptrs)
         self.peer_cnt = arr(*[p + self.cnt_off for p in ptrs])
+        self.peer_flag = arr(*[p + self.flag_off for p in ptrs])
         self.peer_ret = arr(*[p + self.ret_off for p in ptrs])
         self.rec = self.buf[:rec_bytes].view(rows, self.rb)
         self.cnt = self.buf[self.cnt_off:self.cnt_off + 4 * world].view(torch.int32)
         self.ret = self.buf[self.ret_off:total].view(torch.float16).view(rows, hidden)
+        self.epoch = 0
         self.buf.zero_()
-        self.handle.barrier(channel=0)
+        # set-up only: no rank may publish an epoch before every rank has cleared its flags
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
 
     def barrier(self):
-        self.handle.barrier(channel=0)
+        self.epoch += 1
+        stream = torch.cuda.current_stream(self.buf.device).cuda_stream
+        _lib.check(_lib.lib().b200_nvfp4_ep_barrier_p2p(self.peer_flag, self.my_rank, self.world, self.epoch,
+                                                        self.limit, stream), "ep_barrier_p2p")
 
 
 class ExpertParallelMoE:
@@ -154,7 +171,7 @@ class ExpertParallelMoE:
 
     def __init__(self, gate_up_weight, gate_up_weight_scale, down_weight, down_weight_scale, num_experts_total: int,
                  group: Optional[dist.ProcessGroup] = None, backend=None, transport: str = "nccl",
-                 max_tokens: int = 0, num_topk: int = 0, emulate=None):
+                 max_tokens: int = 0, num_topk: int = 0, emulate=None, barrier_limit_cycles: int = 0):
         self.gw, self.gws, self.dw, self.dws = gate_up_weight, gate_up_weight_scale, down_weight, down_weight_scale
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -180,7 +197,8 @@ class ExpertParallelMoE:
             if max_tokens <= 0 or num_topk <= 0:
                 raise ValueError("the p2p transport needs max_tokens (tokens per rank per call) and num_topk")
             hidden = gate_up_weight.shape[2] * 2
-            self.peers = _PeerBuffers(group, self.world, int(max_tokens), hidden, int(num_topk), gate_up_weight.device)
+            self.peers = _PeerBuffers(group, self.world, int(max_tokens), hidden, int(num_topk), gate_up_weight.device,
+                                      self.rank, barrier_limit_cycles)
 
     def _all_to_all_rows(self, send, send_splits, recv_splits):
         recv = torch.empty((sum(recv_splits), send.shape[1]), dtype=send.dtype, device=send.device)
@@ -238,7 +256,7 @@ class ExpertParallelMoE:
         return ret_pos
 
     @torch.no_grad()
-    def p2p_compute_and_return(self):
+    def p2p_compute_and_return(self, mark=None):
         """Phase 2: the routed layer over this rank's experts on everything its slots received, the
         partial rows stored into the source ranks' return slots."""
         w, pb = self.world, self.peers
@@ -270,9 +288,13 @@ class ExpertParallelMoE:
             ws["dout"].data_ptr(), ws["din"].data_ptr(), self.dw.data_ptr(), ws["seq"].data_ptr(), ws["cu"].data_ptr(),
             ws["din_s"].data_ptr(), self.dws.data_ptr(), None, None, None, self.e_local, total, hidden, inter, m_pad,
             avg, 1, None, stream), "grouped_gemm (down)")
+        if mark is not None:
+            mark("routed_layer")
         _lib.check(L.b200_nvfp4_ep_reduce_return_p2p(pb.peer_ret, ws["dout"].data_ptr(), ws["pos"].data_ptr(),
                                                      ws["wts"].data_ptr(), pb.cnt.data_ptr(), self.rank, w, pb.slot_rows,
                                                      hidden, k, stream), "ep_reduce_return_p2p")
+        if mark is not None:
+            mark("reduce_and_return")
 
     @torch.no_grad()
     def p2p_finish(self, ret_pos, out_bf16: bool = True):
@@ -282,17 +304,31 @@ class ExpertParallelMoE:
             self._ones = torch.ones((t, w), dtype=torch.float32, device=ret_pos.device)
         return self.backend.reduce(self.peers.ret, ret_pos, self._ones, out_bf16)
 
-    def _forward_p2p(self, x, topk_ids, topk_weights, out_bf16: bool):
+    def _forward_p2p(self, x, topk_ids, topk_weights, out_bf16: bool, phase_events=None):
+        def mark(name):
+            if phase_events is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                phase_events.append((name, ev))
+
+        mark("start")
         ret_pos = self.p2p_dispatch(x, topk_ids, topk_weights)
+        mark("dispatch")
         self.peers.barrier()
-        self.p2p_compute_and_return()
+        mark("barrier_after_dispatch")
+        self.p2p_compute_and_return(mark)
         self.peers.barrier()
-        return self.p2p_finish(ret_pos, out_bf16)
+        mark("barrier_after_return")
+        out = self.p2p_finish(ret_pos, out_bf16)
+        mark("sum")
+        return out
 
     @torch.no_grad()
-    def forward(self, x, topk_ids, topk_weights, out_bf16: bool = True):
+    def forward(self, x, topk_ids, topk_weights, out_bf16: bool = True, phase_events=None):
+        """phase_events: optional list; the p2p transport appends (phase name, CUDA event) pairs
+        recorded on the current stream after each phase of the layer."""
         if self.transport == "p2p":
-            return self._forward_p2p(x, topk_ids, topk_weights, out_bf16)
+            return self._forward_p2p(x, topk_ids, topk_weights, out_bf16, phase_events)
         w, be = self.world, self.backend
         t, hidden = x.shape
         k = topk_ids.shape[1]

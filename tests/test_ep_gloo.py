@@ -170,3 +170,45 @@ def test_expert_parallel_matches_single_process_oracle(tmp_path, world):
     mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         assert (tmp_path / f"rank{r}.txt").read_text() == "ok"
+
+
+def _leaving_worker(rank, world, port, result_dir):
+    """Rank 1 runs one layer and leaves (between steps, nothing of its own in flight); rank 0's next
+    layer must end with an error inside the process-group timeout, not wait for ever."""
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    outcome = "no error"
+    try:
+        from sm120_nvfp4_b200.ep import ExpertParallelMoE
+        experts, hidden, inter, gw, gws, dw, dws, per_rank = _case(world)
+        e_local = experts // world
+        sl = slice(rank * e_local, (rank + 1) * e_local)
+        layer = ExpertParallelMoE(torch.from_numpy(gw[sl].copy()), torch.from_numpy(gws[sl].copy()),
+                                  torch.from_numpy(dw[sl].copy()), torch.from_numpy(dws[sl].copy()), experts,
+                                  backend=OracleBackend())
+        xb, ids, w = per_rank[rank]
+        x = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16)
+        layer.forward(x, torch.from_numpy(ids), torch.from_numpy(w), out_bf16=False)     # step 0: both ranks
+        if rank == 1:
+            outcome = "left"
+        else:
+            try:
+                layer.forward(x, torch.from_numpy(ids), torch.from_numpy(w), out_bf16=False)   # step 1: alone
+            except Exception as exc:      # the exchange reports the missing peer
+                outcome = "raised " + type(exc).__name__
+    finally:
+        Path(result_dir, f"rank{rank}.txt").write_text(outcome)
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_a_rank_that_leaves_between_steps_ends_the_next_exchange_with_an_error(tmp_path):
+    world = 2
+    port = 29400 + os.getpid() % 200
+    mp.spawn(_leaving_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    assert (tmp_path / "rank1.txt").read_text() == "left"
+    assert (tmp_path / "rank0.txt").read_text().startswith("raised")

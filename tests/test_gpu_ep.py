@@ -143,3 +143,30 @@ def test_peer_memory_hand_off_emulated_on_one_gpu(backend, world):
             got = out.cpu().numpy().astype(np.float32)
             frob = np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)
             assert frob < 2e-2, (call, r, frob)
+
+
+def test_barrier_wait_runs_out_and_reports_the_late_rank(backend):
+    # The cross-GPU barrier of the peer-memory transport with a peer that never arrives: rank 0 of a
+    # two-rank flag set on one GPU, rank 1's flag is simply never written. The wait gives up after
+    # its limit (about half a millisecond here), the launch returns, the device error word names the
+    # late rank, reading it clears it, and once the flag is there the same barrier passes.
+    import ctypes
+    from sm120_nvfp4_b200 import _lib
+    L = _lib.lib()
+    world = 2
+    flags = [torch.zeros(world, dtype=torch.int32, device="cuda") for _ in range(world)]
+    table = (ctypes.c_void_p * world)(*[f.data_ptr() for f in flags])
+    stream = torch.cuda.current_stream().cuda_stream
+    assert L.b200_nvfp4_ep_barrier_p2p(table, 0, world, 1, 1 << 20, stream) == _lib.STATUS_SUCCESS
+    torch.cuda.synchronize()
+    assert _lib.device_error() == (9 | (1 << 8))        # code 9, waiting for rank 1
+    assert _lib.device_error() == 0                      # read-and-clear
+    assert flags[0].tolist() == [1, 0] and flags[1].tolist() == [1, 0]   # rank 0 published its epoch
+    flags[0][1] = 1                                      # "rank 1 arrived"
+    assert L.b200_nvfp4_ep_barrier_p2p(table, 0, world, 1, 1 << 20, stream) == _lib.STATUS_SUCCESS
+    torch.cuda.synchronize()
+    assert _lib.device_error() == 0
+    # argument checks: a rank outside the world, a null table entry
+    assert L.b200_nvfp4_ep_barrier_p2p(table, 2, world, 1, 0, stream) == _lib.STATUS_INVALID_ARGUMENT
+    bad = (ctypes.c_void_p * world)(flags[0].data_ptr(), None)
+    assert L.b200_nvfp4_ep_barrier_p2p(bad, 0, world, 1, 0, stream) == _lib.STATUS_INVALID_ARGUMENT

@@ -262,7 +262,7 @@ def test_full_moe_random_vs_oracle(ops, tokens, experts, topk, hidden, inter, ra
     assert np.isfinite(got).all() and num / den < 2e-2, num / den
 
 
-@pytest.mark.parametrize("tokens,experts,topk", [(4096, 256, 8), (77, 8, 3), (5, 40, 40), (300, 1000, 6)])
+@pytest.mark.parametrize("tokens,experts,topk", [(4096, 256, 8), (77, 8, 3), (5, 40, 40), (300, 1000, 6), (9, 4096, 8)])
 def test_router_topk_bit_exact(ops, tokens, experts, topk):
     # sigmoid scores, top-k with ties to the lower id, renormalised weights: ids and weight bits
     rng = np.random.default_rng(tokens + experts)
@@ -276,6 +276,27 @@ def test_router_topk_bit_exact(ops, tokens, experts, topk):
     np.testing.assert_array_equal(w.cpu().numpy().view(np.uint32), want_w.view(np.uint32))
     assert np.allclose(want_w.sum(1), 1.0, atol=1e-5)
     assert (np.sort(want_ids, axis=1)[:, 1:] != np.sort(want_ids, axis=1)[:, :-1]).all()
+
+
+def test_router_at_the_expert_limit_and_after_a_rejected_call(ops):
+    # 4096 experts need 128 KiB of dynamic shared memory (above the 48 KiB default: the library opts
+    # in once per device); one more expert is rejected before any launch, and the call after a
+    # rejected one succeeds - no launch error is left behind for an unrelated call to report.
+    from sm120_nvfp4_b200 import _lib
+    L = _lib.lib()
+    t, k = 3, 4
+    ids = torch.zeros((t, k), dtype=torch.int32, device="cuda")
+    w = torch.zeros((t, k), dtype=torch.float32, device="cuda")
+    big = torch.randn((t, 4104), dtype=torch.float32, device="cuda")
+    assert L.b200_nvfp4_moe_router_topk(big.data_ptr(), ids.data_ptr(), w.data_ptr(), t, 4104, k, None) == \
+        _lib.STATUS_INVALID_ARGUMENT
+    logits = big[:, :4096].contiguous()
+    assert L.b200_nvfp4_moe_router_topk(logits.data_ptr(), ids.data_ptr(), w.data_ptr(), t, 4096, k, None) == \
+        _lib.STATUS_SUCCESS
+    torch.cuda.synchronize()
+    want_ids, _ = oracle.router_topk(logits.cpu().numpy(), k)
+    np.testing.assert_array_equal(ids.cpu().numpy(), want_ids)
+    assert _lib.device_error() == 0
 
 
 def test_pack_weights_matches_row_quantiser(ops):

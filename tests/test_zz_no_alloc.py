@@ -80,3 +80,41 @@ def test_static_scratch_limit_is_enforced_without_launching(L):
     # exactly at the limit is accepted (checked on shape arithmetic only: M*N*split == 4 Mi)
     assert 4 * 128 * 8192 == limit
     _run_both(L, 128, 8192, 512, 4, seed=4400)
+
+
+def test_static_scratch_entry_leaves_device_memory_untouched(L):
+    # "allocates nothing", measured: the driver's count of free device memory is the same before and
+    # after calls of the entry point (first use of the kernels happened in the tests above; the
+    # operands and the output are allocated before the first reading).
+    m, n, k, split = 128, 1024, 2048, 4
+    a, sfa, b, sfb = _case(m, n, k, 4500)
+    da, db, dsfa, dsfb = _dev(a), _dev(b), _dev(sfa), _dev(sfb)
+    out = torch.empty((m, n), dtype=torch.float16, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        assert L.b200_nvfp4_gemm_splitk_static(m, n, k, split, da.data_ptr(), db.data_ptr(), dsfa.data_ptr(),
+                                               dsfb.data_ptr(), out.data_ptr(), stream) == 0
+        torch.cuda.synchronize()
+
+    call()                                               # any first-use set-up happens here
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        call()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+
+
+def test_static_scratch_rejects_sizes_that_would_overflow(L):
+    # M and N near 2^31 with a large split: the element count does not fit 64 bits; the call must be
+    # refused on arithmetic alone (no launch), and an over-large split_k is an invalid argument
+    from sm120_nvfp4_b200 import _lib
+    before = _lib.launch_count()
+    buf = torch.zeros(16, dtype=torch.uint8, device="cuda")
+    p = buf.data_ptr()
+    huge = (1 << 31) - 8
+    assert L.b200_nvfp4_gemm_splitk_static(huge, huge, 1 << 30, 1 << 22, p, p, p, p, p, None) == 3
+    assert L.b200_nvfp4_gemm_splitk_static(128, 128, 256, 3, p, p, p, p, p, None) == 1      # > ceil(256 / 128) splits
+    ws = torch.zeros(16, dtype=torch.float32, device="cuda")
+    assert L.b200_nvfp4_gemm_splitk(huge, huge, 1 << 30, 1 << 22, p, p, p, p, p, ws.data_ptr(), 64, None) == 3
+    assert _lib.launch_count() == before
