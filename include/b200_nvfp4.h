@@ -361,11 +361,15 @@ B200_NVFP4_API int b200_nvfp4_device_error(int* code);
  * value. */
 B200_NVFP4_API int b200_nvfp4_set_tile_n(int tile_n);
 
-/* Debug aid: copies the first `count` (<= 2048) 64-bit time stamps the GEMM kernel recorded
- * when the environment variable B200_NVFP4_DEBUG has bit 64 set (first two CTAs, first 64
- * pipeline iterations; layout ((cta*8 + role)*64 + iter)*2 + {before, after}; SM clock
- * cycles). SYNCHRONISES. No counterpart in the reference. */
-B200_NVFP4_API int b200_nvfp4_debug_trace(unsigned long long* out, int count);
+/* Test hook for the bounded waits of the GEMM kernel (no counterpart in the reference). Every
+ * mbarrier wait in the kernel gives up after limit_cycles SM clocks (0 restores the default, about
+ * one second); a wait that gives up makes its CTA drain, free its tensor memory and store
+ * code | (CTA index << 8) in the device error word (codes: 1 operand stage not released, 2 / 5
+ * accumulator not handed back, 3 operand stage never ready, 4 tile never finished). With
+ * withhold_one_arrival != 0 the NEXT launch (only) leaves out one barrier arrival on purpose - its
+ * first k-stage never becomes ready - so that a test can watch a wait run out without anything
+ * faulting: that launch returns after the limit, its output is undefined, the error word is set. */
+B200_NVFP4_API int b200_nvfp4_set_wait_limit(long long limit_cycles, int withhold_one_arrival);
 
 /* Number of kernel launches this library has issued from the calling process since load
  * (for launch accounting in benchmarks). No counterpart in the reference. */

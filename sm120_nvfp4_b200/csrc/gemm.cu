@@ -15,7 +15,6 @@
 namespace b200 {
 
 __device__ int g_device_error = 0;
-__device__ unsigned long long g_trace[2048];
 
 int* device_error_word() {
   constexpr int kMaxDevices = 64;
@@ -35,6 +34,11 @@ int* device_error_word() {
 std::atomic<long long> g_launch_count{0};
 
 std::atomic<int> g_tile_n_override{0};
+
+// Test hook (b200_nvfp4_set_wait_limit): wait limit of the kernels launched from now on, and a
+// one-shot request to withhold one barrier arrival in the next launch.
+std::atomic<long long> g_wait_limit{kDefaultWaitLimit};
+std::atomic<int> g_withhold_once{0};
 
 namespace {
 
@@ -88,12 +92,24 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   if (!kTwoCta && s.seqlens == nullptr && s.num_groups == 1 && s.m_uniform < kBlockM)
     a_box_rows = (s.m_uniform + 7) / 8 * 8;
   const int a_sub_bytes = a_box_rows * kStageKBytes;
-  CUtensorMap tmap_a, tmap_b;
+  CUtensorMap tmap_a, tmap_b, tmap_sfa, tmap_sfb;
   const uint64_t row_bytes = static_cast<uint64_t>(s.k) / 2;
+  // Scale regions as rank-3 tensors: 128 words of one 512-byte atom, atoms along K, 128-row atom
+  // rows (all groups' regions follow each other at a whole number of atom rows). One box = the
+  // atoms of a k-stage for one 128-row tile (B: for the one or two scale tiles of a B tile).
+  const uint64_t kt = (static_cast<uint64_t>(s.k) + 63) / 64;
+  const long long atom_row_bytes = static_cast<long long>(kt) * kAtomBytes;
+  const int sfa_group_atom_rows = static_cast<int>(s.sfa_group_stride / atom_row_bytes);
+  const int sfb_group_atom_rows = static_cast<int>(s.sfb_group_stride / atom_row_bytes);
+  const int b_groups = s.b_group_rows > 0 ? s.b_rows_total / s.b_group_rows : 1;
   if (!encode_tmap_2d_u8(&tmap_a, s.a, static_cast<uint64_t>(s.a_rows_total), row_bytes, a_box_rows,
                          kStageKBytes, CU_TENSOR_MAP_SWIZZLE_128B) ||
       !encode_tmap_2d_u8(&tmap_b, s.b, static_cast<uint64_t>(s.b_rows_total), row_bytes,
-                         kSwiGlu ? 128 : Cfg::kBRows, kStageKBytes, CU_TENSOR_MAP_SWIZZLE_128B)) {
+                         kSwiGlu ? 128 : Cfg::kBRows, kStageKBytes, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !encode_tmap_sf(&tmap_sfa, s.sfa, kt, static_cast<uint64_t>(s.num_groups) * sfa_group_atom_rows,
+                      Cfg::kAtomsPerStage, 1) ||
+      !encode_tmap_sf(&tmap_sfb, s.sfb, kt, static_cast<uint64_t>(b_groups) * sfb_group_atom_rows,
+                      Cfg::kAtomsPerStage, kSwiGlu ? 1 : Cfg::kSfbGroups)) {
     return B200_NVFP4_CUDA_ERROR;
   }
 
@@ -116,11 +132,8 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   p.m_uniform = s.m_uniform;
   p.seqlens = s.seqlens;
   p.cu_seqlens = s.cu_seqlens;
-  p.sfa = static_cast<const uint8_t*>(s.sfa);
-  p.sfb = static_cast<const uint8_t*>(s.sfb);
-  p.sfa_group_stride = s.sfa_group_stride;
-  p.sfa_atom_rows = static_cast<int>(s.sfa_group_stride / (static_cast<long long>(scale_k_padded(s.k)) * 128));
-  p.sfb_group_stride = s.sfb_group_stride;
+  p.sfa_group_atom_rows = sfa_group_atom_rows;
+  p.sfb_group_atom_rows = s.b_group_rows > 0 ? sfb_group_atom_rows : 0;
   p.b_group_rows = s.b_group_rows;
   p.out = s.out;
   p.out_split_stride = s.out_split_stride;
@@ -136,11 +149,8 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   p.q_scale_group_stride = s.q_scale_group_stride;
   p.a_sub_bytes = a_sub_bytes;
   p.num_stages = Cfg::stages_for(s.num_groups, a_sub_bytes);
-  p.num_sf_slots = Cfg::sf_slots_for(s.num_groups, a_sub_bytes);
-  static const int debug_flags = [] { const char* e = std::getenv("B200_NVFP4_DEBUG"); return e ? std::atoi(e) : 0; }();
-  p.debug = debug_flags;
-  p.trace = nullptr;
-  if (p.debug & 64) { void* tp = nullptr; if (cudaGetSymbolAddress(&tp, g_trace) == cudaSuccess) p.trace = static_cast<unsigned long long*>(tp); }
+  p.wait_limit = g_wait_limit.load(std::memory_order_relaxed);
+  p.withhold_first_arrival = g_withhold_once.exchange(0, std::memory_order_relaxed);
 
   // One persistent worker (a CTA, or a pair of CTAs) per SM (or per SM pair).
   const int n_tiles = kSwiGlu ? s.swiglu_inter / 128 : (s.n + BN - 1) / BN;
@@ -185,7 +195,7 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   attrs[0].val.clusterDim.z = 1;
   config.attrs = attrs;
   config.numAttrs = 1;
-  const cudaError_t launched = cudaLaunchKernelEx(&config, kernel, tmap_a, tmap_b, tmap_out, p);
+  const cudaError_t launched = cudaLaunchKernelEx(&config, kernel, tmap_a, tmap_b, tmap_out, tmap_sfa, tmap_sfb, p);
   count_launch();
   const int status = launch_status();
   return launched == cudaSuccess ? status : B200_NVFP4_CUDA_ERROR;
@@ -573,9 +583,11 @@ int b200_nvfp4_set_tile_n(int tile_n) {
   return B200_NVFP4_SUCCESS;
 }
 
-int b200_nvfp4_debug_trace(unsigned long long* out, int count) {
-  if (out == nullptr || count <= 0 || count > 2048) return B200_NVFP4_INVALID_ARGUMENT;
-  return cudaMemcpyFromSymbol(out, b200::g_trace, sizeof(unsigned long long) * count) == cudaSuccess ? B200_NVFP4_SUCCESS : B200_NVFP4_CUDA_ERROR;
+int b200_nvfp4_set_wait_limit(long long limit_cycles, int withhold_one_arrival) {
+  if (limit_cycles < 0) return B200_NVFP4_INVALID_ARGUMENT;
+  b200::g_wait_limit.store(limit_cycles > 0 ? limit_cycles : b200::kDefaultWaitLimit, std::memory_order_relaxed);
+  b200::g_withhold_once.store(withhold_one_arrival != 0 ? 1 : 0, std::memory_order_relaxed);
+  return B200_NVFP4_SUCCESS;
 }
 
 long long b200_nvfp4_launch_count(void) {

@@ -67,6 +67,20 @@ bool encode_tmap_2d_u8(CUtensorMap* map, const void* base, uint64_t rows, uint64
   return r == CUDA_SUCCESS;
 }
 
+bool encode_tmap_sf(CUtensorMap* map, const void* base, uint64_t kt, uint64_t atom_rows, uint32_t box_atoms,
+                    uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr || kt == 0 || atom_rows == 0) return false;
+  cuuint64_t dims[3] = {128, kt, atom_rows};
+  cuuint64_t strides[2] = {512, kt * 512};
+  cuuint32_t box[3] = {128, box_atoms, box_rows};
+  cuuint32_t elem_strides[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(base), dims, strides, box,
+                  elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 // Rank-2 tiled map over a row-major matrix of 2- or 4-byte elements (store side: no L2
 // promotion).
 bool encode_tmap_2d_out(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,

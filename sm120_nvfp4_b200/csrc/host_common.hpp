@@ -36,6 +36,12 @@ bool encode_tmap_2d_u8(CUtensorMap* map, const void* base, uint64_t rows, uint64
 bool encode_tmap_2d_out(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                         bool is_f32, uint32_t box_rows, uint32_t box_cols);
 
+// Rank-3 tiled map over block-scaled scale regions: {128 32-bit words of one 512-byte atom,
+// `kt` atoms along K, `atom_rows` 128-row atom rows}, box {128, box_atoms, box_rows}, no swizzle.
+// Boxes that reach past an extent are completed with zeros.
+bool encode_tmap_sf(CUtensorMap* map, const void* base, uint64_t kt, uint64_t atom_rows, uint32_t box_atoms,
+                    uint32_t box_rows);
+
 // Device word written by kernels whose bounded waits time out. One per loaded library.
 int* device_error_word();
 

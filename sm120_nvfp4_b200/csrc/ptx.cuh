@@ -1,6 +1,9 @@
-// Inline-PTX wrappers for the sm_100a features the GEMM kernels use:
-// mbarrier, TMA (tiled and untiled bulk copies), tensor memory (TMEM)
-// allocation, tcgen05.mma / cp / ld / commit, and the UMMA descriptors.
+// Inline-PTX wrappers for the sm_100a features the GEMM kernel uses: mbarrier, TMA (tiled loads
+// and stores), tensor memory (TMEM) allocation, tcgen05.mma / cp / ld / commit, and the UMMA
+// descriptors. Shared-memory operands are 32-bit shared-window addresses throughout: the role
+// loops of the kernel are chains of dependent scalar instructions, and a ring position that
+// advances by a 32-bit add costs less than a generic pointer that needs 64-bit arithmetic and a
+// conversion before every use.
 #pragma once
 
 #include <cstdint>
@@ -31,8 +34,8 @@ __device__ __forceinline__ bool elect_one() {
 
 // ---------------------------------------------------------------- mbarrier
 
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
 
 __device__ __forceinline__ void fence_barrier_init() {
@@ -44,55 +47,62 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
-               "r"(bytes)
-               : "memory");
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+// Arrive on a barrier given by its shared::cluster address (this or another CTA of the cluster).
+// Default (CTA-scope release) semantics: a cluster-scope release costs the arriving thread more
+// than a microsecond, and what these arrivals order - tensor-memory traffic - is ordered by the
+// tcgen05 fences on both sides.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
 }
 
 // Non-blocking probe of the same condition (never suspends the thread).
-__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
 }
 
-// Bounded wait. Every wait in these kernels gives up after ~2^31 clock cycles
-// (about a second), records `code` in *abort_flag (shared) and returns false, so a
-// protocol bug can never hang the GPU. Once the flag is set all later waits return
-// at once.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-                                          volatile int* abort_flag, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
+// Bounded wait. Every wait in the kernel gives up after `limit` clock cycles (about a second by
+// default), records `code` in *abort_flag (shared) and returns false, so a protocol bug can never
+// hang the GPU. Once the flag is set all later waits return at once. The common case - the phase
+// is already complete - is a single non-blocking probe, which returns in less than half the time
+// of try_wait.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                          long long limit) {
+  if (mbar_test_wait(bar, parity)) return true;
   long long start = clock64();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 255u) == 0) {
       if (*abort_flag != 0) return false;
-      if (clock64() - start > (1ll << 31)) {
+      if (clock64() - start > limit) {
         atomicCAS(const_cast<int*>(abort_flag), 0, code);
         return false;
       }
@@ -108,43 +118,50 @@ __device__ __forceinline__ void prefetch_tensormap(const void* desc) {
 
 // 2-D tiled load global -> shared, completion counted in bytes on `bar`.
 // c0 (innermost coordinate) times the element size must be a multiple of 16 bytes.
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* desc, uint64_t* bar,
-                                            int c0, int c1) {
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void* desc, uint32_t bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
-      "l"(reinterpret_cast<uint64_t>(desc)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_dst),
+      "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
 }
 
 // Same load issued by a CTA of a pair (cta_group::2): the data goes to this CTA's shared
 // memory, the completion bytes to the mbarrier at shared::cluster address `bar_cluster_addr`,
-// which may belong to the other CTA of the pair. No multicast: each CTA loads its own tile.
-__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* desc,
-                                                 uint32_t bar_cluster_addr, int c0, int c1) {
+// which may belong to the other CTA of the pair. Each CTA loads its own tile.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const void* desc, uint32_t bar_cluster_addr,
+                                                 int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
+      "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_dst),
       "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
       : "memory");
 }
 
-// Untiled bulk copy global -> shared. Both addresses 16-byte aligned, bytes % 16 == 0.
-__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes,
-                                          uint64_t* bar) {
+// 3-D variants (scale-factor atoms: word inside the atom, atom along K, 128-row atom row).
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const void* desc, uint32_t bar, int c0, int c1,
+                                            int c2) {
   asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
-          "r"(smem_u32(smem_dst)),
-      "l"(reinterpret_cast<uint64_t>(gmem_src)), "r"(bytes), "r"(smem_u32(bar))
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_dst),
+      "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const void* desc, uint32_t bar_cluster_addr,
+                                                 int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_dst),
+      "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
 
 // 2-D tiled store shared -> global (bulk async-group completion).
-__device__ __forceinline__ void tma_store_2d(const void* desc, const void* smem_src, int c0,
-                                             int c1) {
+__device__ __forceinline__ void tma_store_2d(const void* desc, uint32_t smem_src, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::
                    "l"(reinterpret_cast<uint64_t>(desc)),
-               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+               "r"(smem_src), "r"(c0), "r"(c1)
                : "memory");
 }
 
@@ -168,14 +185,14 @@ __device__ __forceinline__ void bulk_wait_group() {
 // instruction acts on this CTA only, 2 = it acts on both CTAs of a pair (a cluster of two
 // CTAs on one TPC that issue one 256-row MMA together).
 
-// Whole-warp call. ncols: power of two in [32, 512]. The base address is written to *smem_out.
-// With kCtas == 2 the same warp of both CTAs must call it.
+// Whole-warp call. ncols: power of two in [32, 512]. The base address is written to shared memory
+// at `smem_out`. With kCtas == 2 the same warp of both CTAs must call it.
 template <int kCtas>
-__device__ __forceinline__ void tmem_alloc(uint32_t* smem_out, uint32_t ncols) {
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_out, uint32_t ncols) {
   if constexpr (kCtas == 2)
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_out)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_out), "r"(ncols) : "memory");
   else
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_out)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_out), "r"(ncols) : "memory");
 }
 
 template <int kCtas>
@@ -206,290 +223,6 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 // kCtas == 2: the arrival is delivered to the barrier at the same shared-memory offset in
 // every CTA of the pair selected by cta_mask (bit i = CTA rank i).
 template <int kCtas>
-__device__ __forceinline__ void tc_commit(uint64_t* bar, uint16_t cta_mask = 1) {
-  if constexpr (kCtas == 2)
-    asm volatile(
-        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
-        "[%0], %1;" ::"r"(smem_u32(bar)), "h"(cta_mask)
-        : "memory");
-  else
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-// Shared -> tensor memory copy of one 32-row x 128-bit block, replicated into the four
-// 32-lane sub-partitions (the form the block-scaled MMA wants for scale factors). With
-// kCtas == 2 each CTA of the pair copies from its own shared memory into its own TMEM.
-template <int kCtas>
-__device__ __forceinline__ void tc_cp_32x128b_warpx4(uint32_t tmem_dst, uint64_t smem_desc) {
-  if constexpr (kCtas == 2)
-    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(smem_desc) : "memory");
-  else
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(smem_desc) : "memory");
-}
-
-// D[tmem] (+)= A[smem] * B[smem]^T with E2M1 operands and one UE4M3 scale per 16 K-elements
-// (K = 64 per instruction). accumulate == 0 overwrites D. kCtas == 2: one 256 x N MMA over
-// the pair; each CTA supplies 128 rows of A and N/2 rows of B from its own shared memory
-// (same offsets in both) and accumulates its 128 rows in its own TMEM.
-template <int kCtas>
-__device__ __forceinline__ void tc_mma_nvfp4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
-                                             uint32_t idesc, uint32_t tmem_sfa, uint32_t tmem_sfb,
-                                             uint32_t accumulate) {
-  if constexpr (kCtas == 2)
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], "
-        "p;\n\t}" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
-        : "memory");
-  else
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], "
-        "p;\n\t}" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
-        : "memory");
-}
-
-// ------------------------------------------------------------------ clusters
-
-__device__ __forceinline__ uint32_t cluster_cta_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-
-// Barrier over all threads of all CTAs in the cluster (release / acquire).
-__device__ __forceinline__ void cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-// shared::cluster address of the object at the same shared-memory offset as `p` in the CTA
-// with rank `cta_rank` of this cluster.
-__device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t cta_rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(cta_rank));
-  return r;
-}
-
-// arrive (count 1) + expect `bytes` more transaction bytes on a barrier given by its
-// shared::cluster address (possibly in the other CTA of the cluster).
-__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t bar_cluster_addr, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(
-                   bar_cluster_addr),
-               "r"(bytes)
-               : "memory");
-}
-
-// Arrives (count 1) on the mbarrier at the same shared-memory offset as `bar` in the CTA
-// with rank `cta_rank` of this cluster. Default (CTA-scope release) semantics: a cluster-scope
-// release costs the arriving thread more than a microsecond, and what these arrivals order -
-// tensor-memory traffic - is ordered by the tcgen05 fences on both sides.
-__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t cta_rank) {
-  asm volatile(
-      "{\n\t.reg .b32 raddr;\n\t"
-      "mapa.shared::cluster.u32 raddr, %0, %1;\n\t"
-      "mbarrier.arrive.shared::cluster.b64 _, [raddr];\n\t}" ::"r"(smem_u32(bar)),
-      "r"(cta_rank)
-      : "memory");
-}
-
-// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives lane (base_lane + t).
-__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-
-// Same, 64 consecutive columns.
-__device__ __forceinline__ void tmem_ld_32x32b_x64(uint32_t taddr, uint32_t (&r)[64]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
-      "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
-      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]),
-        "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]),
-        "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]),
-        "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
-        "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]),
-        "=r"(r[63])
-      : "r"(taddr)
-      : "memory");
-}
-
-// Register -> tensor memory: thread t of the warp writes r[0..N) into N consecutive columns of
-// lane (base_lane + t). The warp may only address its own 32-lane quarter.
-__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-      "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-      "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_st_wait() {
-  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void tmem_ld_wait() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// ------------------------------------------------------------- descriptors
-
-// Shared-memory matrix descriptor (64 bit) for tcgen05.mma / tcgen05.cp:
-//   [0,14)  start address >> 4          [16,30) leading-dimension byte offset >> 4
-//   [32,46) stride-dimension byte offset >> 4   [46,48) descriptor version (1 on sm_100)
-//   [61,64) swizzle mode: 0 none, 2 = 128-byte, 4 = 64-byte, 6 = 32-byte
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes, uint32_t swizzle_mode) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3fffu);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(swizzle_mode & 7u) << 61;
-  return d;
-}
-
-// K-major operand tile whose rows are 128 bytes (256 E2M1 values) written by TMA with the
-// 128-byte swizzle: 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
-  return make_smem_desc(smem_addr, 16, 1024, 2);
-}
-
-// One 512-byte scale-factor atom: 32 rows x 16 bytes, unswizzled, 8-row groups 128 bytes apart.
-__device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
-  return make_smem_desc(smem_addr, 0, 128, 0);
-}
-
-// Instruction descriptor of the block-scaled MMA (kind::mxf4nvf4): E2M1 x E2M1, UE4M3 scales,
-// both operands K-major, FP32 accumulate, M x N x 64.
-//   [7,10) A format (1 = E2M1)   [10,13) B format   [15] A major   [16] B major
-//   [17,23) N >> 3   [23] scale format (0 = UE4M3)   [24,29) M >> 4
-//   [4,6) / [29,31) scale-factor byte ids (0 with four scales per row per instruction)
-__host__ __device__ constexpr uint32_t make_idesc_nvfp4(int m, int n) {  // m = 128, or 256 for a CTA pair
-  return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
-         (static_cast<uint32_t>(m >> 4) << 24);
-}
-
-// ------------------------------------------------ 32-bit shared-address variants
-//
-// The role loops of the GEMM kernel are chains of dependent scalar instructions; every
-// instruction on such a chain costs several cycles, so the loops keep barrier and buffer
-// addresses as 32-bit shared-window addresses that advance by an add per k-stage, instead of
-// generic pointers that need 64-bit arithmetic and a conversion before every use.
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-
-// Arrive on a barrier given by its shared::cluster address (this or another CTA of the cluster).
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
-  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-// Bounded wait (see mbar_wait above). The common case - the phase is already complete - is a
-// single non-blocking probe, which returns in less than half the time of try_wait.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-  if (mbar_test_wait(bar, parity)) return true;
-  long long start = clock64();
-  uint32_t spins = 0;
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 255u) == 0) {
-      if (*abort_flag != 0) return false;
-      if (clock64() - start > (1ll << 31)) {
-        atomicCAS(const_cast<int*>(abort_flag), 0, code);
-        return false;
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void* desc, uint32_t bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_dst),
-      "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1)
-      : "memory");
-}
-
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const void* desc, uint32_t bar_cluster_addr,
-                                                 int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_dst),
-      "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
-      : "memory");
-}
-
-__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gmem_src, uint32_t bytes, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_dst),
-      "l"(reinterpret_cast<uint64_t>(gmem_src)), "r"(bytes), "r"(bar)
-      : "memory");
-}
-
-template <int kCtas>
 __device__ __forceinline__ void tc_commit(uint32_t bar, uint16_t cta_mask = 1) {
   if constexpr (kCtas == 2)
     asm volatile(
@@ -500,21 +233,34 @@ __device__ __forceinline__ void tc_commit(uint32_t bar, uint16_t cta_mask = 1) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta_rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
-  return r;
+// Shared -> tensor memory copy of one scale-factor atom: 32 rows x 128 bits, replicated into the
+// four 32-lane quarters (the form the block-scaled MMA wants). The source is named by a
+// shared-memory matrix descriptor given as its two 32-bit halves. With kCtas == 2 each CTA of the
+// pair copies from its own shared memory (same offset) into its own tensor memory. The copy is
+// ordered with the tcgen05.mma instructions the same thread issues before and after it.
+template <int kCtas>
+__device__ __forceinline__ void tc_cp_32x128b_warpx4(uint32_t tmem_dst, uint32_t desc_lo, uint32_t desc_hi) {
+  if constexpr (kCtas == 2)
+    asm volatile(
+        "{\n\t.reg .b64 d;\n\t"
+        "mov.b64 d, {%1, %2};\n\t"
+        "tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], d;\n\t}" ::"r"(tmem_dst), "r"(desc_lo), "r"(desc_hi)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .b64 d;\n\t"
+        "mov.b64 d, {%1, %2};\n\t"
+        "tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d;\n\t}" ::"r"(tmem_dst), "r"(desc_lo), "r"(desc_hi)
+        : "memory");
 }
 
-__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
-}
-
-// Block-scaled MMA whose shared-memory descriptors are given as their low words (start address
-// and leading-dimension offset) plus one high word common to both (stride offset, version,
-// swizzle): advancing along K or to the next stage is a 32-bit add on the low word.
+// D[tmem] (+)= A[smem] * B[smem]^T with E2M1 operands and one UE4M3 scale per 16 K-elements
+// (K = 64 per instruction). accumulate == 0 overwrites D. kCtas == 2: one 256 x N MMA over
+// the pair; each CTA supplies 128 rows of A and N/2 rows of B from its own shared memory
+// (same offsets in both) and accumulates its 128 rows in its own TMEM. The shared-memory
+// descriptors are given as their low words (start address and leading-dimension offset) plus one
+// high word common to both (stride offset, version, swizzle): advancing along K or to the next
+// stage is a 32-bit add on the low word.
 template <int kCtas>
 __device__ __forceinline__ void tc_mma_nvfp4(uint32_t tmem_d, uint32_t desc_a_lo, uint32_t desc_b_lo,
                                              uint32_t desc_hi, uint32_t idesc, uint32_t tmem_sfa,
@@ -541,11 +287,90 @@ __device__ __forceinline__ void tc_mma_nvfp4(uint32_t tmem_d, uint32_t desc_a_lo
         : "memory");
 }
 
-// Low / high words of the K-major 128-byte-swizzle descriptor (make_kmajor_sw128_desc).
+// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives lane (base_lane + t).
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ------------------------------------------------------------------ clusters
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// Barrier over all threads of all CTAs in the cluster (release / acquire).
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// shared::cluster address of the object at shared-memory address `smem_addr` of this CTA, seen in
+// the CTA with rank `cta_rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
+  return r;
+}
+
+// Stores / loads through a shared::cluster address (distributed shared memory).
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+// ------------------------------------------------------------- descriptors
+//
+// Shared-memory matrix descriptor (64 bit) for tcgen05.mma / tcgen05.cp:
+//   [0,14)  start address >> 4          [16,30) leading-dimension byte offset >> 4
+//   [32,46) stride-dimension byte offset >> 4   [46,48) descriptor version (1 on sm_100)
+//   [61,64) swizzle mode: 0 none, 2 = 128-byte, 4 = 64-byte, 6 = 32-byte
+
+// K-major operand tile whose rows are 128 bytes (256 E2M1 values) written by TMA with the
+// 128-byte swizzle: 8-row groups are 1024 bytes apart (leading-dimension offset 16 bytes).
+constexpr uint32_t kKmajorSw128LboBits = (16u >> 4) << 16;
 __device__ __forceinline__ uint32_t kmajor_sw128_desc_lo(uint32_t smem_addr) {
-  return ((smem_addr >> 4) & 0x3fffu) | ((16u >> 4) << 16);
+  return ((smem_addr >> 4) & 0x3fffu) | kKmajorSw128LboBits;
 }
 constexpr uint32_t kKmajorSw128DescHi = ((1024u >> 4) & 0x3fffu) | (1u << 14) | (2u << 29);
+
+// One 512-byte scale-factor atom: 32 rows x 16 bytes, unswizzled, 8-row groups 128 bytes apart.
+constexpr uint32_t kSfAtomDescHi = ((128u >> 4) & 0x3fffu) | (1u << 14);
+
+// Instruction descriptor of the block-scaled MMA (kind::mxf4nvf4): E2M1 x E2M1, UE4M3 scales,
+// both operands K-major, FP32 accumulate, M x N x 64.
+//   [7,10) A format (1 = E2M1)   [10,13) B format   [15] A major   [16] B major
+//   [17,23) N >> 3   [23] scale format (0 = UE4M3)   [24,29) M >> 4
+//   [4,6) / [29,31) scale-factor byte ids (0 with four scales per row per instruction)
+__host__ __device__ constexpr uint32_t make_idesc_nvfp4(int m, int n) {  // m = 128, or 256 for a CTA pair
+  return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
 
 }  // namespace ptx
 }  // namespace b200

@@ -230,3 +230,31 @@ def test_host_memory_gemm_matches_oracle(ops, m, n, k, block_rows, block_cols):
     torch.cuda.synchronize()
     assert torch.equal(out, first)
     _no_device_error()
+
+
+@pytest.mark.parametrize("tile_n", [64, 512])
+def test_a_wait_that_runs_out_is_reported_and_leaves_the_library_usable(ops, tile_n):
+    # The bounded-wait path of the GEMM kernel, exercised without anything faulting: the test hook
+    # shortens the wait limit to about a millisecond and makes the next launch leave out one
+    # barrier arrival, so the first k-stage of CTA 0 never becomes ready. The launch must return,
+    # the device error word must name a wait code and CTA 0, reading it must clear it, and the
+    # following ordinary launch must be correct (tensor memory was freed, nothing is left armed).
+    from sm120_nvfp4_b200 import _lib
+    L = _lib.lib()
+    L.b200_nvfp4_set_tile_n(tile_n)
+    m, n, k = 256, 512, 1024
+    a, sfa, b, sfb = _random_case(m, n, k, 777)
+    da, db, dsfa, dsfb = _dev(a), _dev(b), _dev(sfa), _dev(sfb)
+    assert L.b200_nvfp4_set_wait_limit(1 << 21, 1) == 0
+    try:
+        ops.cute_gemm(da, db, dsfa, dsfb)
+        torch.cuda.synchronize()
+    finally:
+        assert L.b200_nvfp4_set_wait_limit(0, 0) == 0
+    err = _lib.device_error()
+    assert err != 0 and (err >> 8) <= 1 and (err & 255) in (1, 2, 3, 4, 5), err    # CTA 0 (or its pair partner)
+    assert _lib.device_error() == 0
+    got = ops.cute_gemm(da, db, dsfa, dsfb).cpu().numpy()
+    ref32, _ = oracle.gemm(a, b, sfa, sfb)
+    check_gemm_parity(got, ref32)
+    _no_device_error()
