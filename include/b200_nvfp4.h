@@ -249,8 +249,8 @@ B200_NVFP4_API int b200_nvfp4_expert_moe(void* output, const void* input, const 
 /* Gate/up grouped GEMM with SiLU(gate) * up and the NVFP4 quantisation fused into its epilogue
  * (no counterpart in the reference, which runs group_gemm_nvfp4_async and
  * act_mul_and_quant_nvfp4_async one after the other, src/fused_moe/fused_moe.cu:52-63; the fused
- * MoE entry points of this library use this kernel when B200_NVFP4_FUSED_GATE_UP=1 is set in the
- * environment - on the measured shapes the two separate kernels are faster). w is [G, 2I, K/2] with the gate rows first;
+ * MoE entry points of this library use this kernel unless b200_nvfp4_set_fused_gate_up(0) was
+ * called). w is [G, 2I, K/2] with the gate rows first;
  * output is packed E2M1 [m, I/2], output_scale one region of output_scale_m_pad rows per group -
  * the bytes the two separate calls produce. intermediate_size must be a multiple of 128
  * (otherwise B200_NVFP4_CUTLASS_NOT_SUPPORTED is returned and nothing is launched). tiles /
@@ -360,6 +360,19 @@ B200_NVFP4_API int b200_nvfp4_device_error(int* code);
  * tuning. No counterpart in the reference. Returns B200_NVFP4_INVALID_ARGUMENT for any other
  * value. */
 B200_NVFP4_API int b200_nvfp4_set_tile_n(int tile_n);
+
+/* out_f32[i] = silu(in_f16[i]) = x / (1 + exp(-x)) exactly as b200_nvfp4_moe_act_mul_and_quant and
+ * the fused gate/up epilogue evaluate it (the reference's silu(), src/fused_moe/activation.cu:17-19,
+ * with this library's fixed-sequence exp): for tests that compare every FP16 input with the CPU
+ * oracle. count must be a multiple of 16, both pointers 16-byte aligned. */
+B200_NVFP4_API int b200_nvfp4_silu_f16(void* out_f32, const void* in_f16, int count, b200_stream_t stream);
+
+/* Chooses how b200_nvfp4_fused_moe / b200_nvfp4_expert_moe make the down projection's input:
+ * enabled != 0 (the default) = b200_nvfp4_grouped_gemm_swiglu_quant, one kernel, gate_up_output
+ * is not written; 0 = the reference's two steps (grouped GEMM into gate_up_output, then
+ * b200_nvfp4_moe_act_mul_and_quant). Both produce the same bytes. Process-wide. No counterpart in
+ * the reference. */
+B200_NVFP4_API int b200_nvfp4_set_fused_gate_up(int enabled);
 
 /* Test hook for the bounded waits of the GEMM kernel (no counterpart in the reference). Every
  * mbarrier wait in the kernel gives up after limit_cycles SM clocks (0 restores the default, about

@@ -5,9 +5,8 @@
 // middle stages on rows that are already expert-major, with the reference's workspace carve
 // (src/fused_moe/fused_moe.cu:76-157). Every stage is enqueued on the caller's stream; no
 // host synchronisation, no allocation.
+#include <atomic>
 #include <cstdint>
-
-#include <cstdlib>
 
 #include "host_common.hpp"
 #include "internal.hpp"
@@ -16,19 +15,19 @@ namespace b200 {
 
 namespace {
 
-// Gate/up GEMM -> down-projection input: the two separate steps of the reference by default. With
-// B200_NVFP4_FUSED_GATE_UP=1 in the environment the SiLU * up and the quantisation run in the GEMM's
-// epilogue instead (one kernel, the FP16 product never reaches memory, gate_up_output stays
-// untouched; same bits). Measured on the DeepSeek-shaped layer the fused form is slower (1.98 ms
-// against 1.71 ms per layer): the exact expf and the two IEEE divisions per value cost ~50
-// instructions, which 8 epilogue warps per SM cannot hide behind the mainloop the way a
-// full-occupancy streaming kernel can.
+// Gate/up GEMM -> down-projection input. Two forms with the same bits: the reference's two steps
+// (grouped GEMM writes the FP16 product, a second kernel reads it back for SiLU * up + the NVFP4
+// quantisation), or one kernel whose epilogue does the activation and the quantisation on the
+// accumulator, so that the FP16 product (256 MiB at the DeepSeek-shaped layer) never reaches
+// memory and gate_up_output stays untouched. b200_nvfp4_set_fused_gate_up chooses; the fused form
+// needs an intermediate size that is a multiple of 128 and falls back to the two steps otherwise.
+std::atomic<int> g_fused_gate_up{1};
+
 int gate_up_stage(void* down_input, void* down_input_scale, void* gate_up_output, const void* x,
                   const void* w, const void* seqlens, const void* cu_seqlens, const void* x_scale,
                   const void* w_scale, void* tiles, void* cu_tiles, int num_expert_local, int total_rows,
                   int intermediate_size, int hidden_size, int m_pad, int avg, cudaStream_t stream) {
-  static const bool fused = [] { const char* e = std::getenv("B200_NVFP4_FUSED_GATE_UP"); return e && e[0] == '1'; }();
-  if (fused) {
+  if (g_fused_gate_up.load(std::memory_order_relaxed) != 0) {
     const int st = gemm_grouped_swiglu(down_input, down_input_scale, x, w, seqlens, cu_seqlens, x_scale, w_scale,
                                        tiles, cu_tiles, num_expert_local, total_rows, intermediate_size,
                                        hidden_size, m_pad, m_pad, avg, stream);
@@ -269,6 +268,15 @@ int b200_nvfp4_expert_moe(void* output, const void* input, const void* input_sca
                           down_weight, down_weight_scale, seqlens, cu_seqlens, workspace,
                           workspace_bytes, total_rows, hidden_size, intermediate_size,
                           num_expert_local, grouped_scale_m_pad, static_cast<cudaStream_t>(stream));
+}
+
+int b200_nvfp4_silu_f16(void* out_f32, const void* in_f16, int count, b200_stream_t stream) {
+  return b200::moe_silu_f16(out_f32, in_f16, count, static_cast<cudaStream_t>(stream));
+}
+
+int b200_nvfp4_set_fused_gate_up(int enabled) {
+  b200::g_fused_gate_up.store(enabled != 0 ? 1 : 0, std::memory_order_relaxed);
+  return B200_NVFP4_SUCCESS;
 }
 
 }  // extern "C"

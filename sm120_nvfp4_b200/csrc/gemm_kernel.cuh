@@ -625,38 +625,70 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
       if constexpr (kSwiGlu) {
         // Accumulator columns 0..127 are the gate, 128..255 the up projection of the same 128
-        // intermediate columns. This warp takes 64 of them (4 blocks of 16): both operands are
-        // rounded to FP16 first - the values the unfused path would have written and read back -
-        // then silu(gate) * up in FP32, quantised per 16 values with one UE4M3 scale.
+        // intermediate columns. This warp takes 64 of them (4 blocks of 16). Both operands are
+        // rounded to FP16 first - the values the unfused path would have written and read back - and
+        // that is also how they wait in registers (64 packed words): the whole slab is read before
+        // any arithmetic, the 64 columns shared with the other accumulator first, so the accumulator
+        // goes back to the MMA warp at once and silu(gate) * up + the quantisation of one tile run
+        // while the next tile is being computed.
         const uint32_t g_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                                 static_cast<uint32_t>(acc * Cfg::kAccStride + half * 64);
+        uint32_t gp[32], up[32];    // gate / up columns 0..63 of this warp as half2 pairs
+        auto load_half = [&](uint32_t addr, uint32_t* packed) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(addr, v);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            packed[i] = pack_half2(__uint_as_float(v[2 * i]) * alpha, __uint_as_float(v[2 * i + 1]) * alpha);
+        };
+        if (reversed) {     // accumulator 0: the shared columns are up columns 64..127 of the tile (second half's)
+          load_half(g_addr + 128, up);
+          load_half(g_addr + 160, up + 16);
+          release_overlap();
+          load_half(g_addr, gp);
+          load_half(g_addr + 32, gp + 16);
+        } else {            // accumulator 1: gate columns 0..63 of the tile (first half's)
+          load_half(g_addr, gp);
+          load_half(g_addr + 32, gp + 16);
+          release_overlap();
+          load_half(g_addr + 128, up);
+          load_half(g_addr + 160, up + 16);
+        }
+        release_accumulator();
+        // Rows behind the end of the group hold whatever the neighbouring rows of A and the unwritten
+        // part of the scale region made of them - possibly NaN or infinity, which send every division
+        // below down its slow path. A slab without a valid row is skipped, and the lanes of invalid
+        // rows compute on zeros.
+        if (t.mt * kTileM + slab_row >= s_rows[t.g]) {
+          acc ^= 1;
+          if (acc == 0) acc_phase ^= 1;
+          continue;
+        }
+        if (!row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { gp[i] = 0u; up[i] = 0u; }
+        }
         uint32_t payload[8];
         uint32_t scale_word = 0;
 #pragma unroll
-        for (int pass = 0; pass < 2; ++pass) {
-          uint32_t gv[32], uv[32];
-          ptx::tmem_ld_32x32b_x32(g_addr + pass * 32, gv);
-          ptx::tmem_ld_32x32b_x32(g_addr + 128 + pass * 32, uv);
-          ptx::tmem_ld_wait();
-          if (pass == 1) {
-            release_overlap();
-            release_accumulator();
-          }
+        for (int b = 0; b < 4; ++b) {
+          float gv[16], uv[16], v[16];
 #pragma unroll
-          for (int b = 0; b < 2; ++b) {
-            float v[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float gf = __half2float(__float2half_rn(__uint_as_float(gv[16 * b + i]) * alpha));
-              const float uf = __half2float(__float2half_rn(__uint_as_float(uv[16 * b + i]) * alpha));
-              v[i] = __fmul_rn(nvfp4_silu(gf), uf);
-            }
-            uint32_t lo, hi;
-            const uint8_t code = quantize_block16(v, lo, hi);
-            payload[(2 * pass + b) * 2] = lo;
-            payload[(2 * pass + b) * 2 + 1] = hi;
-            scale_word |= static_cast<uint32_t>(code) << (8 * (2 * pass + b));
+          for (int i = 0; i < 8; ++i) {
+            const __half2 g2 = *reinterpret_cast<const __half2*>(&gp[8 * b + i]);
+            const __half2 u2 = *reinterpret_cast<const __half2*>(&up[8 * b + i]);
+            gv[2 * i] = __low2float(g2);
+            gv[2 * i + 1] = __high2float(g2);
+            uv[2 * i] = __low2float(u2);
+            uv[2 * i + 1] = __high2float(u2);
           }
+          silu_mul_block16(gv, uv, v);
+          uint32_t lo, hi;
+          const uint8_t code = quantize_block16(v, lo, hi);
+          payload[2 * b] = lo;
+          payload[2 * b + 1] = hi;
+          scale_word |= static_cast<uint32_t>(code) << (8 * b);
         }
         if (row_ok) {
           const int inter = p.swiglu_inter;

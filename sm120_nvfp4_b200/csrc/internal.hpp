@@ -59,6 +59,8 @@ int moe_move_rows(void* dst, const void* src, const void* index, int count, int 
 int moe_router_topk(const void* logits, void* topk_ids, void* topk_weights, int num_tokens,
                     int num_experts, int num_topk, cudaStream_t stream);
 
+int moe_silu_f16(void* out_f32, const void* in_f16, int count, cudaStream_t stream);
+
 int moe_reduce(void* output, const void* down_output, const void* topk_pos, const void* topk_scale,
                const void* shared_output, int num_tokens, int hidden_size, int num_topk,
                bool out_is_bf16, cudaStream_t stream);

@@ -291,8 +291,7 @@ quant_rows_kernel(uint8_t* __restrict__ output, uint8_t* __restrict__ output_sca
         float g[16], u[16];
         load16(gate, g);
         load16(gate + width, u);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = __fmul_rn(nvfp4_silu(g[i]), u[i]);
+        silu_mul_block16(g, u, v);
       } else if constexpr (kMode == 1) {
         load16(static_cast<const __half*>(input) + in_row * width + kb * 16, v);
       } else {
@@ -455,6 +454,23 @@ move_rows_kernel(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src,
     uint4* d4 = reinterpret_cast<uint4*>(dst + dst_row * row_bytes);
     for (int v = lane; v < vecs; v += 32) d4[v] = s4[v];
   }
+}
+
+// out[i] = silu(in[i]) for FP16 inputs, sixteen per thread through silu_mul_block16 (up = 1): the
+// activation exactly as the quantising kernels and the fused GEMM epilogue evaluate it, exposed so
+// that a test can compare every FP16 input with the oracle.
+__global__ void __launch_bounds__(256)
+silu_f16_kernel(float* __restrict__ out, const __half* __restrict__ in, int blocks16) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= blocks16) return;
+  float g[16], u[16], v[16];
+  load16(in + static_cast<long long>(b) * 16, g);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) u[i] = 1.0f;
+  silu_mul_block16(g, u, v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    reinterpret_cast<float4*>(out + static_cast<long long>(b) * 16)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -649,6 +665,18 @@ int moe_router_topk(const void* logits, void* topk_ids, void* topk_weights, int 
   router_topk_kernel<<<blocks, 256, static_cast<size_t>(8) * num_experts * sizeof(float), stream>>>(
       static_cast<const float*>(logits), static_cast<int*>(topk_ids), static_cast<float*>(topk_weights),
       num_tokens, num_experts, num_topk);
+  count_launch();
+  return launch_status();
+}
+
+int moe_silu_f16(void* out_f32, const void* in_f16, int count, cudaStream_t stream) {
+  if (out_f32 == nullptr || in_f16 == nullptr || count <= 0 || (count % 16) != 0 || !aligned16(out_f32) ||
+      !aligned16(in_f16)) {
+    return B200_NVFP4_INVALID_ARGUMENT;
+  }
+  const int blocks16 = count / 16;
+  silu_f16_kernel<<<(blocks16 + 255) / 256, 256, 0, stream>>>(static_cast<float*>(out_f32),
+                                                             static_cast<const __half*>(in_f16), blocks16);
   count_launch();
   return launch_status();
 }

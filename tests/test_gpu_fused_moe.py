@@ -200,6 +200,75 @@ def test_quantize_expert_parity(ops, golden_dir, is_bf16):
     np.testing.assert_array_equal(packed.cpu().numpy(), o_packed)
 
 
+def test_silu_is_bit_exact_on_every_fp16_input(ops):
+    # The activation as the kernels evaluate it (branch-free form inside +-87, the plain form outside)
+    # against the oracle's x / (1 + exp(-x)) on all 65536 FP16 bit patterns: same FP32 bits, NaN for NaN.
+    from sm120_nvfp4_b200 import _lib
+    L = _lib.lib()
+    bits = np.arange(65536, dtype=np.uint16)
+    x = torch.from_numpy(bits.view(np.int16)).cuda().view(torch.float16)
+    out = torch.empty(65536, dtype=torch.float32, device="cuda")
+    assert L.b200_nvfp4_silu_f16(out.data_ptr(), x.data_ptr(), 65536, _stream()) == 0
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    Lo = oracle.lib()
+    xf = bits.view(np.float16).astype(np.float32)
+    want = np.array([Lo.oracle_silu(float(v)) for v in xf], dtype=np.float32)
+    nan = np.isnan(want)
+    assert np.array_equal(np.isnan(got), nan)
+    np.testing.assert_array_equal(got[~nan].view(np.uint32), want[~nan].view(np.uint32))
+    # a block that mixes in-range and out-of-range gates takes the plain form for all sixteen values
+    mixed = np.tile(np.array([1.5, -200.0, 0.25, 90.0, -88.0, -3.0, 65504.0, -65504.0], np.float16), 2)
+    xm = torch.from_numpy(mixed).cuda()
+    om = torch.empty(16, dtype=torch.float32, device="cuda")
+    assert L.b200_nvfp4_silu_f16(om.data_ptr(), xm.data_ptr(), 16, _stream()) == 0
+    torch.cuda.synchronize()
+    wm = np.array([Lo.oracle_silu(float(v)) for v in mixed.astype(np.float32)], dtype=np.float32)
+    np.testing.assert_array_equal(om.cpu().numpy().view(np.uint32), wm.view(np.uint32))
+
+
+def _boundary_rows():
+    """FP16 rows that put values exactly on, one ulp above and one ulp below every E2M1 rounding
+    boundary (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5 times the block's decoded scale) for every UE4M3
+    scale, both signs, plus infinities and a signed zero: the cases where a quotient computed any
+    other way than the reference's IEEE division could round differently."""
+    bounds = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0]
+    rows = []
+    for code in range(1, 0x7f):
+        e, m = code >> 3, code & 7
+        d = m / 512.0 if e == 0 else (8 + m) / 8.0 * 2.0 ** (e - 7)
+        head = np.float16(6.0 * d)                    # amax = 6 d: the block's scale decodes to d exactly
+        if not np.isfinite(head) or float(head) != 6.0 * d:
+            continue
+        vals = []
+        for b in bounds:
+            c = np.float16(b * d)
+            vals += [c, np.nextafter(c, np.float16(np.inf)), np.nextafter(c, np.float16(0))]
+        blocks = [[head] + vals[:15], [head] + vals[15:] + [np.float16(0)] * 9]
+        row = []
+        for blk in blocks:
+            row += blk
+        row += [-v for v in row]
+        rows.append(np.array(row, np.float16))
+    special = np.zeros(64, np.float16)
+    special[0], special[1], special[2], special[3] = np.inf, -np.inf, -0.0, 1.0      # a block with infinities
+    special[16], special[17] = 3.0, -0.0                                             # a signed zero in a finite block
+    rows.append(special)
+    return np.stack(rows)
+
+
+def test_row_quantiser_is_exact_on_every_rounding_boundary(ops):
+    x = _boundary_rows()
+    rows, hidden = x.shape
+    counts = np.array([rows], np.int32)
+    cu = np.array([0, rows], np.int32)
+    pad = (rows + 127) // 128 * 128
+    packed, scales = ops.quantize_expert(_dev(x), _dev(counts), _dev(cu), scale_m_pad=pad)
+    o_packed, o_scales = oracle.quantize_expert(x.view(np.uint16), counts, cu, pad, False)
+    np.testing.assert_array_equal(scales.cpu().numpy(), o_scales)
+    np.testing.assert_array_equal(packed.cpu().numpy(), o_packed)
+
+
 @pytest.mark.parametrize("with_shared", [True, False])
 def test_reduce_bit_exact(ops, with_shared):
     from sm120_nvfp4_b200 import _lib
