@@ -81,6 +81,16 @@ B200_NVFP4_API int b200_nvfp4_gemm_splitk(int m, int n, int k, int split_k, cons
                                           void* c_f16, void* workspace, size_t workspace_bytes,
                                           b200_stream_t stream);
 
+/* The same split-K GEMM with the partial tiles reduced on the chip (no counterpart in the
+ * reference): the split_k (2 or 4) CTAs of a cluster compute the K ranges b200_nvfp4_gemm_splitk
+ * uses, exchange the FP32 partial tiles through distributed shared memory, add them in split order
+ * and round once to FP16 - the bits of b200_nvfp4_gemm_splitk on the same operands - in one launch,
+ * without a workspace and without a round trip of partial sums through HBM. The default dispatcher
+ * uses it for its M == 128 / 256 paths. */
+B200_NVFP4_API int b200_nvfp4_gemm_splitk_cluster(int m, int n, int k, int split_k, const void* a,
+                                                  const void* b, const void* sfa, const void* sfb,
+                                                  void* c_f16, b200_stream_t stream);
+
 /* Split-K GEMM for callers that cannot hand over a workspace and must not allocate one: a
  * plugin hook that receives only operand pointers and a stream, a runtime whose memory plan
  * is frozen, a serving loop that may not touch the device allocator (an allocation can
@@ -119,7 +129,9 @@ B200_NVFP4_API int b200_nvfp4_gemm_host(int m, int n, int k, const void* a_host,
                                         void* c_dev, int block_rows, int block_cols,
                                         b200_stream_t stream);
 
-/* nvfp4_gemm_sm120 (src/gemm/gemm_dispatch.cu:63-90): default dispatcher. */
+/* nvfp4_gemm_sm120 (src/gemm/gemm_dispatch.cu:63-90): default dispatcher. The M == 128 / 256 paths
+ * require the workspace of b200_nvfp4_gemm_workspace_bytes as the reference does (status 3 without
+ * it) and compute the split-K result on chip (b200_nvfp4_gemm_splitk_cluster, same bits). */
 B200_NVFP4_API int b200_nvfp4_gemm_auto(int m, int n, int k, const void* a, const void* b,
                                         const void* sfa, const void* sfb, void* c_f16,
                                         void* workspace, size_t workspace_bytes,

@@ -28,6 +28,7 @@ _SIGNATURES = {
     "b200_nvfp4_gemm_workspace_bytes": (C.c_size_t, [ci, ci, ci]),
     "b200_nvfp4_gemm": (ci, [ci, ci, ci, ci, vp, vp, vp, vp, vp, ci, vp]),
     "b200_nvfp4_gemm_splitk": (ci, [ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, C.c_size_t, vp]),
+    "b200_nvfp4_gemm_splitk_cluster": (ci, [ci, ci, ci, ci, vp, vp, vp, vp, vp, vp]),
     "b200_nvfp4_gemm_splitk_static_max_elements": (C.c_size_t, []),
     "b200_nvfp4_gemm_splitk_static": (ci, [ci, ci, ci, ci, vp, vp, vp, vp, vp, vp]),
     "b200_nvfp4_gemm_host": (ci, [ci, ci, ci] + [vp] * 10 + [ci, ci, vp]),

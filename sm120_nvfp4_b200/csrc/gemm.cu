@@ -67,16 +67,19 @@ struct LaunchSpec {
   int expected_m_tiles;    // estimate used to pick the tile width and the grid
   bool exact_m_tiles;      // expected_m_tiles is exact (dense) rather than a hint (grouped)
   int avg_group_rows;      // rows per group (exact for dense, a hint for grouped)
+  int cluster_split = 1;   // 2 / 4: K ranges of a tile on the CTAs of a cluster, reduced on chip (FP16 out)
   int swiglu_inter = 0;    // fused gate/up: intermediate size I (n == 2 * I), else 0
   void* q_out = nullptr;
   void* q_scale = nullptr;
   long long q_scale_group_stride = 0;
 };
 
-template <int BN, bool F32, bool kTwoCta, bool kSwiGlu = false>
+template <int BN, bool F32, bool kTwoCta, bool kSwiGlu = false, int kClusterSplit = 1>
 int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t stream) {
   using Cfg = GemmCfg<BN, kTwoCta>;
-  auto kernel = nvfp4_gemm_kernel<BN, F32, kTwoCta, kSwiGlu>;
+  auto kernel = nvfp4_gemm_kernel<BN, F32, kTwoCta, kSwiGlu, kClusterSplit>;
+  constexpr int kClusterCtas = Cfg::kCtas * kClusterSplit;
+  constexpr int kRedBytes = Cfg::red_bytes(kClusterSplit);
   static std::once_flag once[64];
   static cudaError_t attr_status[64];
   std::call_once(once[dev.device], [&] {
@@ -148,34 +151,35 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   p.q_scale = static_cast<uint8_t*>(s.q_scale);
   p.q_scale_group_stride = s.q_scale_group_stride;
   p.a_sub_bytes = a_sub_bytes;
-  p.num_stages = Cfg::stages_for(s.num_groups, a_sub_bytes);
+  p.num_stages = Cfg::stages_for(s.num_groups, a_sub_bytes, kRedBytes);
+  p.red_bytes = kRedBytes;
   p.wait_limit = g_wait_limit.load(std::memory_order_relaxed);
   p.withhold_first_arrival = g_withhold_once.exchange(0, std::memory_order_relaxed);
 
   // One persistent worker (a CTA, or a pair of CTAs) per SM (or per SM pair).
   const int n_tiles = kSwiGlu ? s.swiglu_inter / 128 : (s.n + BN - 1) / BN;
   const long long m_tiles = kTwoCta ? (s.expected_m_tiles + 1) / 2 : s.expected_m_tiles;
-  long long tasks = m_tiles * n_tiles * s.num_splits;
-  int workers = dev.sm_count / Cfg::kCtas;
-  if (kTwoCta) {
+  long long tasks = m_tiles * n_tiles * (kClusterSplit > 1 ? 1 : s.num_splits);
+  int workers = dev.sm_count / kClusterCtas;
+  if (kClusterCtas > 1) {
     // Not every SM need be pairable: ask how many pairs can be resident at once, so the
     // persistent grid never queues a pair behind a running one.
     static std::once_flag pair_once[64];
     static int max_pairs[64];
     std::call_once(pair_once[dev.device], [&] {
       cudaLaunchConfig_t probe = {};
-      probe.gridDim = dim3(static_cast<unsigned>(dev.sm_count));
+      probe.gridDim = dim3(static_cast<unsigned>(dev.sm_count / kClusterCtas * kClusterCtas));
       probe.blockDim = dim3(kGemmThreads);
       probe.dynamicSmemBytes = kSmemBudget;
       cudaLaunchAttribute attr[1];
       attr[0].id = cudaLaunchAttributeClusterDimension;
-      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.x = kClusterCtas;
       attr[0].val.clusterDim.y = 1;
       attr[0].val.clusterDim.z = 1;
       probe.attrs = attr;
       probe.numAttrs = 1;
       int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, kernel, &probe) != cudaSuccess || n < 1) n = dev.sm_count / 2;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &probe) != cudaSuccess || n < 1) n = dev.sm_count / (2 * kClusterCtas);
       max_pairs[dev.device] = n;
     });
     if (workers > max_pairs[dev.device]) workers = max_pairs[dev.device];
@@ -184,13 +188,13 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   if (workers < 1) workers = 1;
 
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(static_cast<unsigned>(workers * Cfg::kCtas));
+  config.gridDim = dim3(static_cast<unsigned>(workers * kClusterCtas));
   config.blockDim = dim3(kGemmThreads);
-  config.dynamicSmemBytes = Cfg::smem_bytes(s.num_groups, a_sub_bytes);
+  config.dynamicSmemBytes = Cfg::smem_bytes(s.num_groups, a_sub_bytes, kRedBytes);
   config.stream = stream;
   cudaLaunchAttribute attrs[1];
   attrs[0].id = cudaLaunchAttributeClusterDimension;
-  attrs[0].val.clusterDim.x = Cfg::kCtas;
+  attrs[0].val.clusterDim.x = kClusterCtas;
   attrs[0].val.clusterDim.y = 1;
   attrs[0].val.clusterDim.z = 1;
   config.attrs = attrs;
@@ -224,12 +228,41 @@ int pick_tile(const LaunchSpec& s, const DeviceInfo& dev) {
   return 64;
 }
 
+// K split over the CTAs of a cluster for a single dense FP16 problem with too few tiles to occupy
+// the GPU: the largest of 4 / 2 whose clusters still fit in one wave and leave every CTA at least
+// two k-stages. (The caller may have fixed the split: the M = 128 / 256 paths of the dispatcher.)
+int pick_cluster_split(const LaunchSpec& s, const DeviceInfo& dev, int tile) {
+  if (s.out_f32 || s.num_splits != 1 || s.num_groups != 1 || s.seqlens != nullptr || s.swiglu_inter != 0 ||
+      (tile != 64 && tile != 128))
+    return 1;
+  const long long tasks = static_cast<long long>(s.expected_m_tiles) * ((s.n + tile - 1) / tile);
+  const int k_stages = (s.k + (tile == 64 ? 511 : 255)) / (tile == 64 ? 512 : 256);
+  for (int split = 4; split >= 2; split /= 2)
+    if (tasks * split <= dev.sm_count && k_stages >= 2 * split) return split;
+  return 1;
+}
+
 int launch_gemm(const LaunchSpec& s, cudaStream_t stream, int force_tile = 0) {
   const DeviceInfo& dev = current_device_info();
   if (!dev.ok) return B200_NVFP4_CUDA_ERROR;
   if (!device_supported(dev)) return B200_NVFP4_UNSUPPORTED_DEVICE;
   int tile = force_tile ? force_tile : pick_tile(s, dev);
   if (tile == 512 && s.out_f32) tile = 256;
+  if (s.cluster_split > 1 && tile > 128) tile = 128;     // the on-chip reduction is built for 64 / 128 columns
+  int split = s.cluster_split > 1 ? s.cluster_split : (s.cluster_split == 1 ? pick_cluster_split(s, dev, tile) : 1);
+  // A skinny problem is bound by what one thread can issue per byte of B (four MMAs and eight scale
+  // copies per 256 values of K, whatever the tile's width): 128-column tiles with K split four ways
+  // move twice the bytes per issued instruction of 64-column tiles split two ways.
+  if (!force_tile && s.cluster_split == 1 && tile == 64 && pick_cluster_split(s, dev, 128) == 4) {
+    tile = 128;
+    split = 4;
+  }
+  if (split > 1) {
+    if (tile == 64) return split == 4 ? launch_instance<64, false, false, false, 4>(s, dev, stream)
+                                      : launch_instance<64, false, false, false, 2>(s, dev, stream);
+    return split == 4 ? launch_instance<128, false, false, false, 4>(s, dev, stream)
+                      : launch_instance<128, false, false, false, 2>(s, dev, stream);
+  }
   switch (tile) {
     case 512:
       return launch_instance<256, false, true>(s, dev, stream);
@@ -351,6 +384,7 @@ int gemm_splitk(int m, int n, int k, int split_k, const void* a, const void* b, 
   s.expected_m_tiles = (m + kBlockM - 1) / kBlockM;
   s.exact_m_tiles = true;
   s.avg_group_rows = m;
+  s.cluster_split = 0;
   int status = launch_gemm(s, stream, env_tile_n());
   if (status != B200_NVFP4_SUCCESS) return status;
   const DeviceInfo& dev = current_device_info();
@@ -362,6 +396,47 @@ int gemm_splitk(int m, int n, int k, int split_k, const void* a, const void* b, 
       static_cast<long long>(m) * n, split_k);
   count_launch();
   return launch_status();
+}
+
+// Split-K whose partial tiles never leave the chip: the CTAs of a cluster take the K ranges of
+// gemm_splitk (same ranges, same FP32 partial sums, added in the same split order, one rounding to
+// FP16 - the result is bit-identical), reduce through distributed shared memory and write C. No
+// workspace, one launch. split_k must be 2 or 4.
+int gemm_splitk_cluster(int m, int n, int k, int split_k, const void* a, const void* b, const void* sfa,
+                        const void* sfb, void* c_f16, cudaStream_t stream) {
+  if (!valid_shape(m, n, k) || (split_k != 2 && split_k != 4) || split_k > (k + 127) / 128 || a == nullptr ||
+      b == nullptr || sfa == nullptr || sfb == nullptr || c_f16 == nullptr || !aligned16(a) || !aligned16(b) ||
+      !aligned16(sfa) || !aligned16(sfb) || !aligned16(c_f16)) {
+    return B200_NVFP4_INVALID_ARGUMENT;
+  }
+  const int skp = scale_k_padded(k);
+  LaunchSpec s{};
+  s.num_groups = 1;
+  s.m_uniform = m;
+  s.a_rows_total = m;
+  s.n = n;
+  s.k = k;
+  s.a = a;
+  s.b = b;
+  s.sfa = sfa;
+  s.sfb = sfb;
+  s.sfa_group_stride = static_cast<long long>(align_up_int(m, 128)) * skp;
+  s.sfb_group_stride = static_cast<long long>(align_up_int(n, 128)) * skp;
+  s.b_group_rows = n;
+  s.b_rows_total = n;
+  s.out = c_f16;
+  s.out_f32 = false;
+  s.num_splits = 1;
+  s.expected_m_tiles = (m + kBlockM - 1) / kBlockM;
+  s.exact_m_tiles = true;
+  s.avg_group_rows = m;
+  s.cluster_split = split_k;
+  // 128-column tiles unless that leaves most SMs without a cluster
+  const DeviceInfo& dev = current_device_info();
+  const long long tasks128 = static_cast<long long>(s.expected_m_tiles) * ((n + 127) / 128);
+  int tile = env_tile_n();
+  if (tile != 64 && tile != 128) tile = (dev.ok && tasks128 * split_k * 2 <= dev.sm_count) ? 64 : 128;
+  return launch_gemm(s, stream, tile);
 }
 
 int gemm_grouped(void* y, const void* x, const void* w, const void* seqlens,
@@ -407,6 +482,7 @@ int gemm_grouped(void* y, const void* x, const void* w, const void* seqlens,
   s.expected_m_tiles = static_cast<int>(est);
   s.exact_m_tiles = false;
   s.avg_group_rows = avg;
+  s.cluster_split = 0;
   return launch_gemm(s, stream, env_tile_n());
 }
 
@@ -531,6 +607,11 @@ int b200_nvfp4_gemm_splitk(int m, int n, int k, int split_k, const void* a, cons
                            static_cast<cudaStream_t>(stream));
 }
 
+int b200_nvfp4_gemm_splitk_cluster(int m, int n, int k, int split_k, const void* a, const void* b,
+                                   const void* sfa, const void* sfb, void* c_f16, b200_stream_t stream) {
+  return b200::gemm_splitk_cluster(m, n, k, split_k, a, b, sfa, sfb, c_f16, static_cast<cudaStream_t>(stream));
+}
+
 int b200_nvfp4_gemm_auto(int m, int n, int k, const void* a, const void* b, const void* sfa,
                          const void* sfb, void* c_f16, void* workspace, size_t workspace_bytes,
                          b200_stream_t stream) {
@@ -538,11 +619,15 @@ int b200_nvfp4_gemm_auto(int m, int n, int k, const void* a, const void* b, cons
   const size_t required = b200_nvfp4_gemm_workspace_bytes(m, n, k);
   if (required != 0 && (workspace == nullptr || workspace_bytes < required))
     return B200_NVFP4_INSUFFICIENT_WORKSPACE;
+  // The reference's M = 128 / 256 paths: split-K 4 / 2 with the partial sums added in split order.
+  // The workspace the reference ABI asks for is still required (same status codes) but not used:
+  // the partial tiles are reduced on chip (b200_nvfp4_gemm_splitk_cluster), with the bits
+  // b200_nvfp4_gemm_splitk gives on the same operands.
   switch (path) {
     case B200_NVFP4_PATH_M128_SPLITK4:
-      return b200_nvfp4_gemm_splitk(m, n, k, 4, a, b, sfa, sfb, c_f16, workspace, workspace_bytes, stream);
+      return b200::gemm_splitk_cluster(m, n, k, 4, a, b, sfa, sfb, c_f16, static_cast<cudaStream_t>(stream));
     case B200_NVFP4_PATH_M256_SPLITK2:
-      return b200_nvfp4_gemm_splitk(m, n, k, 2, a, b, sfa, sfb, c_f16, workspace, workspace_bytes, stream);
+      return b200::gemm_splitk_cluster(m, n, k, 2, a, b, sfa, sfb, c_f16, static_cast<cudaStream_t>(stream));
     default:
       return b200_nvfp4_gemm(1, m, n, k, a, b, sfa, sfb, c_f16, 0, stream);
   }

@@ -38,6 +38,11 @@
 // the next. 256-column tiles have no room for two disjoint ones beside the scales (512 columns of
 // tensor memory): theirs overlap by 64 columns, the epilogue drains those 64 first and hands them
 // back early (`ovl_free`), the rest while the next tile is being computed.
+// Split-K for skinny problems (kClusterSplit = 2 or 4): the CTAs of a cluster compute the same output
+// tile over consecutive K ranges and reduce the FP32 partial tiles among themselves through
+// distributed shared memory - each CTA collects one column slice of the tile from its peers, adds
+// the partials in split order and writes that slice - so all SMs pull on the weights of a problem
+// with few tiles, without a workspace, a second launch or a round trip of partial sums through HBM.
 // All mbarrier waits are bounded (ptx::mbar_wait); a timeout is reported through
 // GemmParams::error instead of hanging.
 #pragma once
@@ -65,12 +70,13 @@ constexpr int kWarpLoadSf = 3;
 constexpr int kFirstEpilogueWarp = 4;
 constexpr int kGemmThreads = 32 * (kFirstEpilogueWarp + kEpilogueWarps);
 constexpr int kMaxStages = 8;
-constexpr int kBarrierBytes = 256;      // 2 x kMaxStages + 5 mbarriers, TMEM base, abort flag
+constexpr int kBarrierBytes = 256;      // 2 x kMaxStages + 7 mbarriers, TMEM base, abort flag
 constexpr int kSmemBudget = 232448;     // 227 KB opt-in limit per CTA
 constexpr long long kDefaultWaitLimit = 1ll << 31;   // clock cycles, about a second
 
 // Codes a timed-out wait leaves in the device error word (low byte; the CTA index above it).
-enum WaitCode { kWaitEmpty = 1, kWaitAccEmpty = 2, kWaitFull = 3, kWaitAccFull = 4, kWaitOverlap = 5 };
+enum WaitCode { kWaitEmpty = 1, kWaitAccEmpty = 2, kWaitFull = 3, kWaitAccFull = 4, kWaitOverlap = 5,
+                kWaitPartials = 7, kWaitSlots = 8 };
 
 struct GemmParams {
   int num_groups;
@@ -101,6 +107,7 @@ struct GemmParams {
   uint8_t* q_out;             // packed E2M1 [rows, I/2]
   uint8_t* q_scale;           // UE4M3 scale regions, one per group, indexed by the row inside the group
   long long q_scale_group_stride;
+  int red_bytes;              // cluster split-K: bytes of the partial-tile slots in shared memory, else 0
   long long wait_limit;       // clock cycles a wait may last (kDefaultWaitLimit)
   int withhold_first_arrival;  // test hook: the scale loader of CTA 0 skips its first arrival, so the
                                // first k-stage never becomes ready and the waits run out
@@ -155,14 +162,17 @@ struct GemmCfg {
   static constexpr int fixed_bytes(int num_groups) {
     return 1024 + kBarrierBytes + 3 * (num_groups + 1) * 4 + kStagingBytes;
   }
-  static constexpr int stages_for(int num_groups, int a_sub_bytes = kABytes) {
+  // Cluster split-K: a CTA keeps one slot of 128 rows x BN / splits FP32 columns per peer.
+  static constexpr int red_bytes(int splits) { return splits > 1 ? (splits - 1) * kBlockM * (BN / splits) * 4 : 0; }
+  static constexpr int stages_for(int num_groups, int a_sub_bytes = kABytes, int extra_bytes = 0) {
     // the MMA reads a full 128-row A block from the last sub-stage, so that much shared memory
     // must follow it: B, the scales and the staging area do
-    int s = (kSmemBudget - fixed_bytes(num_groups)) / stage_bytes(a_sub_bytes);
+    int s = (kSmemBudget - fixed_bytes(num_groups) - extra_bytes) / stage_bytes(a_sub_bytes);
     return s > kMaxStages ? kMaxStages : s;
   }
-  static constexpr int smem_bytes(int num_groups, int a_sub_bytes = kABytes) {
-    return fixed_bytes(num_groups) + stages_for(num_groups, a_sub_bytes) * stage_bytes(a_sub_bytes);
+  static constexpr int smem_bytes(int num_groups, int a_sub_bytes = kABytes, int extra_bytes = 0) {
+    return fixed_bytes(num_groups) + extra_bytes +
+           stages_for(num_groups, a_sub_bytes, extra_bytes) * stage_bytes(a_sub_bytes);
   }
   static_assert(stages_for(kMaxGroups) >= 3, "pipeline too shallow");
 };
@@ -202,7 +212,7 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <int BN, bool kOutF32, bool kTwoCta, bool kSwiGlu = false>
+template <int BN, bool kOutF32, bool kTwoCta, bool kSwiGlu = false, int kClusterSplit = 1>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b,
@@ -211,6 +221,10 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_sfb, const GemmParams p) {
   using Cfg = GemmCfg<BN, kTwoCta>;
   static_assert(!kSwiGlu || (BN == 256 && !kOutF32), "the fused gate/up epilogue is built on 256-column FP16 tiles");
+  static_assert(kClusterSplit == 1 || (!kTwoCta && !kSwiGlu && !kOutF32 && BN <= 128 &&
+                                       (kClusterSplit == 2 || kClusterSplit == 4)),
+                "cluster split-K: single-CTA FP16 tiles of 64 or 128 columns, 2 or 4 splits");
+  constexpr bool kSplitCluster = kClusterSplit > 1;
   constexpr int kCtas = Cfg::kCtas;
   constexpr int kTileM = Cfg::kTileM;
   constexpr int kSub = Cfg::kSub;
@@ -230,13 +244,18 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // empty:     the copies and MMAs that read the stage are done
   // acc_full:  an accumulator holds a finished tile          acc_empty: the epilogue has read all of it
   // ovl_free:  (overlapping accumulators) the epilogue has read the 64 columns the other accumulator shares
-  uint64_t* bars = reinterpret_cast<uint64_t*>(staging_base + Cfg::kStagingBytes);
+  // red_full:  (cluster split-K) every peer has stored its partial of this CTA's column slice
+  // red_empty: (cluster split-K) every peer has read the partials this CTA stored into it
+  uint8_t* red_base = staging_base + Cfg::kStagingBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(red_base + p.red_bytes);
   const uint32_t full_u32 = ptx::smem_u32(bars);
   const uint32_t empty_u32 = full_u32 + 8 * kMaxStages;
   const uint32_t acc_full_u32 = empty_u32 + 8 * kMaxStages;
   const uint32_t acc_empty_u32 = acc_full_u32 + 16;
   const uint32_t ovl_free_u32 = acc_empty_u32 + 16;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 5);
+  const uint32_t red_full_u32 = ovl_free_u32 + 8;
+  const uint32_t red_empty_u32 = red_full_u32 + 8;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 7);
   int* abort_flag = reinterpret_cast<int*>(tmem_holder + 1);
   int* s_cu_tiles = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + kBarrierBytes);
   int* s_row0 = s_cu_tiles + (p.num_groups + 1);
@@ -251,9 +270,20 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int G = p.num_groups;
   const uint32_t cta_rank = kTwoCta ? ptx::cluster_cta_rank() : 0u;
   const bool leader = cta_rank == 0;
-  const int worker = static_cast<int>(blockIdx.x) / kCtas;     // CTA or CTA pair
-  const int num_workers = static_cast<int>(gridDim.x) / kCtas;
+  const int split_rank = kSplitCluster ? static_cast<int>(ptx::cluster_cta_rank()) : 0;   // this CTA's K range
+  constexpr int kClusterCtas = kCtas * kClusterSplit;
+  const int worker = static_cast<int>(blockIdx.x) / kClusterCtas;     // CTA, CTA pair or split-K cluster
+  const int num_workers = static_cast<int>(gridDim.x) / kClusterCtas;
+  const int num_splits = kSplitCluster ? kClusterSplit : p.num_splits;   // K ranges per tile
+  const int task_splits = kSplitCluster ? 1 : p.num_splits;              // ... that are tasks of their own
 
+  // every warp that will use a tensor map fetches its descriptor now, in parallel with the set-up
+  if (lane == 0) {
+    if (warp == kWarpLoadA) ptx::prefetch_tensormap(&tmap_a);
+    if (warp == kWarpLoadB) ptx::prefetch_tensormap(&tmap_b);
+    if (warp == kWarpLoadSf) { ptx::prefetch_tensormap(&tmap_sfa); ptx::prefetch_tensormap(&tmap_sfb); }
+    if (warp == kFirstEpilogueWarp && p.tma_store) ptx::prefetch_tensormap(&tmap_out);
+  }
   // ---- group tables: valid rows, first row and m-tile prefix of every group
   for (int g = threadIdx.x; g < G; g += kGemmThreads) {
     int rows = p.seqlens ? p.seqlens[g] : p.m_uniform;
@@ -263,8 +293,20 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     s_cu_tiles[g] = (rows + kTileM - 1) / kTileM;
   }
   // Set-up runs in parallel: the lanes of warp 0 initialise one barrier each, the MMA warp
-  // allocates tensor memory meanwhile. A single problem (one group) needs no scan of tile counts
-  // and therefore only one block-wide barrier before the pipeline starts.
+  // allocates tensor memory meanwhile. A single problem (one group) needs no scan of tile counts;
+  // its loaders start as soon as the barriers exist, without waiting for the tensor-memory
+  // allocation (`fast_start`): on a skinny problem the first bytes from HBM are the critical path.
+  const bool fast_start = !kTwoCta && G == 1;
+  if (G == 1 && threadIdx.x == 0) {   // this thread wrote the only table entry itself
+    const int tiles = s_cu_tiles[0];
+    s_cu_tiles[0] = 0;
+    s_cu_tiles[1] = tiles;
+    if (blockIdx.x == 0) {
+      const int t128 = (s_rows[0] + kBlockM - 1) / kBlockM;
+      if (p.tiles_out) p.tiles_out[0] = t128;
+      if (p.cu_tiles_out) { p.cu_tiles_out[0] = 0; p.cu_tiles_out[1] = t128; }
+    }
+  }
   if (warp == 0) {
     if (lane == 0) *abort_flag = 0;
     for (int s = lane; s < kStages; s += 32) {
@@ -276,31 +318,33 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ptx::mbar_init(acc_empty_u32 + 8 * lane, kEpilogueWarps * kCtas);
     }
     if (lane == 2) ptx::mbar_init(ovl_free_u32, (kEpilogueWarps / 2) * kCtas);
+    if (lane == 3) ptx::mbar_init(red_full_u32, 1);     // the announcing thread; the partials arrive as counted bytes
+    if (lane == 4) ptx::mbar_init(red_empty_u32, kEpilogueWarps * (kClusterSplit - 1) + (kSplitCluster ? 0 : 1));
     __syncwarp();
-    if (lane == 0) {
-      ptx::fence_barrier_init();
-      ptx::prefetch_tensormap(&tmap_a);
-      ptx::prefetch_tensormap(&tmap_b);
-      ptx::prefetch_tensormap(&tmap_sfa);
-      ptx::prefetch_tensormap(&tmap_sfb);
-      if (p.tma_store) ptx::prefetch_tensormap(&tmap_out);
+    if (lane == 0) ptx::fence_barrier_init();
+  }
+  const bool loader_warp = warp == kWarpLoadA || warp == kWarpLoadB || warp == kWarpLoadSf;
+  if (fast_start) {
+    // Two named barriers over the whole CTA. 1 = "barriers and tables exist": everybody arrives, only
+    // the loaders wait for it. 2 = "tensor memory allocated": everybody arrives (the loaders at once),
+    // the MMA and epilogue warps wait.
+    if (loader_warp) {
+      ptx::named_barrier_sync(1, kGemmThreads);
+      ptx::named_barrier_arrive(2, kGemmThreads);
+    } else {
+      ptx::named_barrier_arrive(1, kGemmThreads);
+      if (warp == kWarpMma) {
+        ptx::tmem_alloc<kCtas>(ptx::smem_u32(tmem_holder), Cfg::kTmemCols);
+        ptx::tmem_relinquish<kCtas>();
+      }
+      ptx::tc_fence_before_sync();
+      ptx::named_barrier_sync(2, kGemmThreads);
     }
   } else if (warp == kWarpMma) {
     ptx::tmem_alloc<kCtas>(ptx::smem_u32(tmem_holder), Cfg::kTmemCols);
     ptx::tmem_relinquish<kCtas>();
   }
-  if (G == 1) {
-    if (threadIdx.x == 0) {   // this thread wrote the only table entry itself
-      const int tiles = s_cu_tiles[0];
-      s_cu_tiles[0] = 0;
-      s_cu_tiles[1] = tiles;
-      if (blockIdx.x == 0) {
-        const int t128 = (s_rows[0] + kBlockM - 1) / kBlockM;
-        if (p.tiles_out) p.tiles_out[0] = t128;
-        if (p.cu_tiles_out) { p.cu_tiles_out[0] = 0; p.cu_tiles_out[1] = t128; }
-      }
-    }
-  } else {
+  if (G > 1) {
     __syncthreads();
     if (warp == kWarpLoadA) {  // exclusive scan of the per-group tile counts, 32 groups at a time
       int carry = 0;
@@ -337,16 +381,25 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
   }
-  ptx::tc_fence_before_sync();
-  __syncthreads();
-  if constexpr (kTwoCta) ptx::cluster_sync();  // the partner's barriers are initialised too
+  if (!fast_start) {
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+  }
+  // The partners' barriers must exist before anything is signalled to them. A pair does so from its
+  // first load on; a split-K cluster only in its epilogues, so its threads just announce themselves
+  // here and wait for the others where they first need them.
+  if constexpr (kTwoCta) {
+    ptx::cluster_arrive_relaxed();
+    ptx::cluster_wait();
+  }
+  if constexpr (kSplitCluster) ptx::cluster_arrive_relaxed();
   ptx::tc_fence_after_sync();
 
   const uint32_t tmem_base = *tmem_holder;
   const int total_mt = s_cu_tiles[G];
   // fused gate/up: a tile covers 128 columns of the intermediate (its gate and its up half)
   const int n_tiles = kSwiGlu ? p.swiglu_inter / 128 : (p.n + BN - 1) / BN;
-  const int total_tasks = total_mt * n_tiles * p.num_splits;
+  const int total_tasks = total_mt * n_tiles * task_splits;
   const int kt = (p.k + 63) / 64;               // scale atoms along K
   const int k_stages = (kt + kAtomsPerStage - 1) / kAtomsPerStage;   // pipeline stages along K
   const int k_stages_full = kt / kAtomsPerStage;                     // k-stages with all their atoms
@@ -377,7 +430,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     bool withhold = role == 2 && p.withhold_first_arrival != 0 && blockIdx.x == 0;
     bool ok = true;
     for (int task = worker; task < total_tasks && ok; task += num_workers) {
-      TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
+      TileCoord t = decode_tile(task, total_mt, n_tiles, task_splits, p.raster_m, s_cu_tiles, G);
+      if constexpr (kSplitCluster) t.split = split_rank;
       int row = 0, row2 = 0;   // A / B: matrix row of the box; scales: atom rows of SFA and SFB
       if (role == 0) {
         row = s_row0[t.g] + t.mt * kTileM + static_cast<int>(cta_rank) * kBlockM;
@@ -388,8 +442,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         row = t.g * p.sfa_group_atom_rows + t.mt * kCtas + static_cast<int>(cta_rank);
         row2 = t.g * p.sfb_group_atom_rows + (kSwiGlu ? t.nt : (t.nt * BN) / 128);
       }
-      const int ks_begin = (k_stages * t.split) / p.num_splits;
-      const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
+      const int ks_begin = (k_stages * t.split) / num_splits;
+      const int ks_end = (k_stages * (t.split + 1)) / num_splits;
       for (int ks = ks_begin; ks < ks_end; ++ks) {
         if (!ptx::mbar_wait(empty_a, phase ^ 1, abort_flag, kWaitEmpty, wait_limit)) { ok = false; break; }
         if (ptx::elect_one()) {
@@ -458,9 +512,10 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t phase = 0, acc_phase = 0, full_a = full_u32, empty_a = empty_u32, a_lo = a_lo0;
       bool ok = true;
       for (int task = worker; task < total_tasks && ok; task += num_workers, ++tile_iter) {
-        TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
-        const int ks_begin = (k_stages * t.split) / p.num_splits;
-        const int ks_end = (k_stages * (t.split + 1)) / p.num_splits;
+        TileCoord t = decode_tile(task, total_mt, n_tiles, task_splits, p.raster_m, s_cu_tiles, G);
+      if constexpr (kSplitCluster) t.split = split_rank;
+        const int ks_begin = (k_stages * t.split) / num_splits;
+        const int ks_end = (k_stages * (t.split + 1)) / num_splits;
         // A tile narrower than 128 columns uses part of a 128-row scale atom: column
         // (n0 % 128) / 32 of the four TMEM columns the atom occupies.
         const uint32_t sfb_sub = BN < 128 ? static_cast<uint32_t>(((t.nt * BN) % 128) / 32) : 0u;
@@ -565,10 +620,12 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     constexpr bool kCanStage = Cfg::kStagingBytes > 0;
     const uint32_t stg = ptx::smem_u32(staging_base) + (warp - kFirstEpilogueWarp) * Cfg::kStagingWarpBytes;
     const uint32_t stg_row = stg + lane * 128;
-    int acc = 0;
+    int acc = 0, tile_iter = 0;
     uint32_t acc_phase = 0;
-    for (int task = worker; task < total_tasks; task += num_workers) {
-      TileCoord t = decode_tile(task, total_mt, n_tiles, p.num_splits, p.raster_m, s_cu_tiles, G);
+    if constexpr (kSplitCluster) ptx::cluster_wait();     // every CTA of the cluster has initialised its barriers
+    for (int task = worker; task < total_tasks; task += num_workers, ++tile_iter) {
+      TileCoord t = decode_tile(task, total_mt, n_tiles, task_splits, p.raster_m, s_cu_tiles, G);
+      if constexpr (kSplitCluster) t.split = split_rank;
       const int slab_row = static_cast<int>(cta_rank) * kBlockM + q * 32;   // first row of the slab in the tile
       const int row_in_tile = slab_row + lane;
       const bool row_ok = t.mt * kTileM + row_in_tile < s_rows[t.g];
@@ -577,7 +634,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int col0 = t.nt * BN + half * kWarpCols;
       // A k-split that owns no k-stage (more splits than stages) contributes zeros: the
       // accumulator was never written, so its contents are replaced, not scaled.
-      const bool empty_split = (k_stages * t.split) / p.num_splits == (k_stages * (t.split + 1)) / p.num_splits;
+      const bool empty_split = (k_stages * t.split) / num_splits == (k_stages * (t.split + 1)) / num_splits;
       const float alpha = p.group_alpha ? p.group_alpha[t.g] : 1.0f;
       const bool staged = kCanStage && p.tma_store != 0 && slab_full;
       // row coordinate of the slab in the output tensor map (split-K slices are stacked)
@@ -623,7 +680,118 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       };
 
-      if constexpr (kSwiGlu) {
+      if constexpr (kSplitCluster) {
+        // Cluster split-K. This CTA holds the partial tile of K range `me`; CTA d of the cluster finishes
+        // columns [d W, (d + 1) W) of the tile. Every warp (32 rows, half of each slice's columns):
+        //   1. stores its part of the other CTAs' slices into their shared memory (one slot per sender;
+        //      16-byte units, swizzled by row) with asynchronous stores that count their bytes on the
+        //      receiver's `red_full` barrier;
+        //   2. keeps its part of this CTA's own slice in registers and hands the accumulator back;
+        //   3. waits for the peers' partials, adds all of them in split order 0 .. S-1 in FP32 (the order
+        //      of the reference's split-K reduction, src/gemm/specialized/m128_gemm.cu:367-382), rounds
+        //      once to FP16 and stores;
+        //   4. tells the peers that their slots may be overwritten (`red_empty`).
+        constexpr int S = kClusterSplit, W = BN / S, HW = W / 2, kRowChunks = W / 4;
+        constexpr uint32_t kSlotBytes = kBlockM * W * 4;
+        const uint32_t red_u32 = ptx::smem_u32(red_base);
+        const int me = split_rank;
+        const int trow = q * 32 + lane;                          // row of the tile this lane holds
+        const uint32_t row_off = static_cast<uint32_t>(trow) * (W * 4);
+        const uint32_t swz = static_cast<uint32_t>(trow & (kRowChunks - 1) & 7);
+        const uint32_t acc_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                  static_cast<uint32_t>(acc * Cfg::kAccStride + half * HW);
+        if (tile_iter > 0 && !ptx::mbar_wait_cluster(red_empty_u32, static_cast<uint32_t>(tile_iter - 1) & 1u,
+                                                     abort_flag, kWaitSlots, wait_limit))
+          break;
+        // One thread announces what this CTA is about to receive: every peer sends the valid rows of
+        // this CTA's slice, 4 W bytes per row, as asynchronous stores that report their bytes to
+        // `red_full` themselves - no fence and no separate signal on the sending side.
+        const int rows_here = min(kBlockM, s_rows[t.g] - t.mt * kTileM);
+        if (warp == kFirstEpilogueWarp && lane == 0)
+          ptx::mbar_arrive_expect_tx(red_full_u32, static_cast<uint32_t>((S - 1) * rows_here * W * 4));
+        // all partial slices for the peers first (one wait for the loads), then the stores
+        uint32_t snd[S - 1][HW];
+#pragma unroll
+        for (int dd = 1; dd < S; ++dd) {
+          const int d = (me + dd) % S;
+#pragma unroll
+          for (int c8 = 0; c8 < HW / 8; ++c8) ptx::tmem_ld_32x32b_x8(acc_addr + d * W + c8 * 8, &snd[dd - 1][c8 * 8]);
+        }
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int dd = 1; dd < S; ++dd) {
+          const int d = (me + dd) % S;
+          const uint32_t remote = ptx::map_to_cta(red_u32 + static_cast<uint32_t>(me < d ? me : me - 1) * kSlotBytes + row_off,
+                                                  static_cast<uint32_t>(d));
+          const uint32_t remote_bar = ptx::map_to_cta(red_full_u32, static_cast<uint32_t>(d));
+          if (row_ok) {
+#pragma unroll
+            for (int c4 = 0; c4 < HW / 4; ++c4) {
+              const uint32_t c = static_cast<uint32_t>((half * HW) / 4 + c4);
+              if (empty_split)
+                ptx::st_async_v4(remote + ((c ^ swz) << 4), 0u, 0u, 0u, 0u, remote_bar);
+              else
+                ptx::st_async_v4(remote + ((c ^ swz) << 4), snd[dd - 1][4 * c4], snd[dd - 1][4 * c4 + 1],
+                                 snd[dd - 1][4 * c4 + 2], snd[dd - 1][4 * c4 + 3], remote_bar);
+            }
+          }
+        }
+        float own[HW];
+        {
+          uint32_t v[HW];
+#pragma unroll
+          for (int c8 = 0; c8 < HW / 8; ++c8) ptx::tmem_ld_32x32b_x8(acc_addr + me * W + c8 * 8, &v[c8 * 8]);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < HW; ++i) own[i] = empty_split ? 0.0f : __uint_as_float(v[i]);
+        }
+        release_accumulator();
+        if (!ptx::mbar_wait_cluster(red_full_u32, static_cast<uint32_t>(tile_iter) & 1u, abort_flag, kWaitPartials,
+                                    wait_limit))
+          break;
+        float sum[HW];
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+          if (s == me) {
+#pragma unroll
+            for (int i = 0; i < HW; ++i) sum[i] = s == 0 ? own[i] : __fadd_rn(sum[i], own[i]);
+          } else {
+            const uint32_t slot = red_u32 + static_cast<uint32_t>(s < me ? s : s - 1) * kSlotBytes + row_off;
+#pragma unroll
+            for (int c4 = 0; c4 < HW / 4; ++c4) {
+              const uint32_t c = static_cast<uint32_t>((half * HW) / 4 + c4);
+              const uint4 v = row_ok ? ptx::ld_shared_v4(slot + ((c ^ swz) << 4)) : make_uint4(0u, 0u, 0u, 0u);
+              const float f[4] = {__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w)};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) sum[c4 * 4 + i] = s == 0 ? f[i] : __fadd_rn(sum[c4 * 4 + i], f[i]);
+            }
+          }
+        }
+        {
+          __half* dst = static_cast<__half*>(p.out) + out_row * p.n + t.nt * BN + me * W + half * HW;
+          const int cbase = t.nt * BN + me * W + half * HW;
+#pragma unroll
+          for (int i = 0; i < HW / 8; ++i) {
+            if (row_ok && cbase + 8 * i < p.n) {
+              uint4 o;
+              o.x = pack_half2(sum[8 * i] * alpha, sum[8 * i + 1] * alpha);
+              o.y = pack_half2(sum[8 * i + 2] * alpha, sum[8 * i + 3] * alpha);
+              o.z = pack_half2(sum[8 * i + 4] * alpha, sum[8 * i + 5] * alpha);
+              o.w = pack_half2(sum[8 * i + 6] * alpha, sum[8 * i + 7] * alpha);
+              *reinterpret_cast<uint4*>(dst + 8 * i) = o;
+            }
+          }
+        }
+        if (task + num_workers < total_tasks) {     // another tile follows: hand the slots back
+          ptx::fence_acq_rel_cluster();      // every lane's reads of the slots, before lane 0 reports them
+          __syncwarp();
+          if (lane == 0) {
+#pragma unroll
+            for (int dd = 1; dd < S; ++dd)
+              ptx::mbar_arrive_release_cluster(ptx::map_to_cta(red_empty_u32, static_cast<uint32_t>((me + dd) % S)));
+          }
+        }
+      } else if constexpr (kSwiGlu) {
         // Accumulator columns 0..127 are the gate, 128..255 the up projection of the same 128
         // intermediate columns. This warp takes 64 of them (4 blocks of 16). Both operands are
         // rounded to FP16 first - the values the unfused path would have written and read back - and
@@ -818,10 +986,13 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 
   // ---- teardown
+  if constexpr (kSplitCluster) {
+    if (warp < kFirstEpilogueWarp) ptx::cluster_wait();   // the epilogue warps did so before their first tile
+  }
   __syncthreads();
   // In a pair neither CTA may leave (or free tensor memory) while the other can still
   // signal its barriers or read its shared memory.
-  if constexpr (kTwoCta) ptx::cluster_sync();
+  if constexpr (kTwoCta || kSplitCluster) ptx::cluster_sync();
   const int aborted = *abort_flag;
   if (aborted != 0) {
     // give copies that may still be in flight time to land before shared memory goes away

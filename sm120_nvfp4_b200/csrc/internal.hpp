@@ -24,6 +24,9 @@ int gemm_splitk(int m, int n, int k, int split_k, const void* a, const void* b, 
                 const void* sfb, void* c_f16, void* workspace, size_t workspace_bytes,
                 cudaStream_t stream);
 
+int gemm_splitk_cluster(int m, int n, int k, int split_k, const void* a, const void* b, const void* sfa,
+                        const void* sfb, void* c_f16, cudaStream_t stream);
+
 int gemm_grouped(void* y, const void* x, const void* w, const void* seqlens,
                  const void* cu_seqlens, const void* x_scale, const void* w_scale, void* tiles,
                  void* cu_tiles, int num_group, int m, int n, int k, int m_scale_pad,

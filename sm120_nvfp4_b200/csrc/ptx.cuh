@@ -88,6 +88,30 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Orders this thread's earlier accesses (including stores into other CTAs' shared memory) before
+// its later ones at cluster scope.
+__device__ __forceinline__ void fence_acq_rel_cluster() {
+  asm volatile("fence.acq_rel.cluster;" ::: "memory");
+}
+
+// Arrival on a barrier of another CTA that publishes this thread's earlier stores into that CTA's
+// shared memory (release at cluster scope): the counterpart of mbar_wait_cluster.
+__device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait_acquire_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait. Every wait in the kernel gives up after `limit` clock cycles (about a second by
 // default), records `code` in *abort_flag (shared) and returns false, so a protocol bug can never
 // hang the GPU. Once the flag is set all later waits return at once. The common case - the phase
@@ -100,6 +124,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 255u) == 0) {
+      if (*abort_flag != 0) return false;
+      if (clock64() - start > limit) {
+        atomicCAS(const_cast<int*>(abort_flag), 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+// The same bounded wait with acquire semantics at cluster scope: what other CTAs of the cluster
+// stored into this CTA's shared memory before their releasing arrivals is visible afterwards.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                                  long long limit) {
+  long long start = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait_acquire_cluster(bar, parity)) return true;
     if ((++spins & 255u) == 0) {
       if (*abort_flag != 0) return false;
       if (clock64() - start > limit) {
@@ -302,6 +344,16 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
       : "memory");
 }
 
+// Same, 8 consecutive columns.
+// (The destination registers hold the data only after tmem_ld_wait(): nothing may read or copy
+// them in between, so callers that batch several loads pass the final destination.)
+__device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -312,6 +364,30 @@ __device__ __forceinline__ uint32_t cluster_cta_rank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
   return r;
+}
+
+// The two halves of the cluster barrier: every thread of every CTA arrives once and waits once per
+// phase, not necessarily at the same place in the program.
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+// Arrival without a release of this thread's earlier writes: enough after set-up, where the only
+// writes the partners must see - the mbarrier initialisations - were published by
+// fence_barrier_init(), and far cheaper than a cluster-scope release.
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Named CTA barriers (ids 1..15; id 0 is __syncthreads): `count` threads take part, each either
+// waits for the others (sync) or only reports (arrive). Whole warps only.
+__device__ __forceinline__ void named_barrier_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void named_barrier_arrive(int id, int count) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
 // Barrier over all threads of all CTAs in the cluster (release / acquire).
@@ -331,6 +407,16 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta_
 // Stores / loads through a shared::cluster address (distributed shared memory).
 __device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+
+// Asynchronous 16-byte store into the shared memory of a CTA of this cluster; on completion it adds
+// 16 to the transaction count of the mbarrier `bar_cluster_addr` (same CTA as the data), so the
+// receiver's wait on that barrier covers the data: no fence or separate arrival by the sender.
+__device__ __forceinline__ void st_async_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d,
+                                            uint32_t bar_cluster_addr) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(addr),
+               "r"(a), "r"(b), "r"(c), "r"(d), "r"(bar_cluster_addr)
                : "memory");
 }
 

@@ -202,9 +202,45 @@ def test_splitk_entry_point_and_workspace_contract(ops):
                                   out.data_ptr(), ws.data_ptr(), ws_bytes, stream) == 0
     torch.cuda.synchronize()
     check_gemm_parity(out.cpu().numpy(), ref32)
-    # the workspace holds the four FP32 partial slices; the output is their sum in split order
+    # the workspace-taking entry leaves the four FP32 partial slices in the workspace; its output is
+    # their sum in split order, and the dispatcher (which reduces the same partial tiles on chip,
+    # through the cluster's shared memory) gives the same bits
+    out2 = torch.empty_like(out)
+    assert L.b200_nvfp4_gemm_splitk(m, n, k, 4, da.data_ptr(), db.data_ptr(), dsfa.data_ptr(), dsfb.data_ptr(),
+                                    out2.data_ptr(), ws.data_ptr(), ws_bytes, stream) == 0
+    torch.cuda.synchronize()
     partial = ws.view(4, m, n).cpu().numpy()
-    np.testing.assert_array_equal(oracle.splitk_reduce(partial), out.cpu().numpy())
+    np.testing.assert_array_equal(oracle.splitk_reduce(partial), out2.cpu().numpy())
+    np.testing.assert_array_equal(out.cpu().numpy(), out2.cpu().numpy())
+    _no_device_error()
+
+
+@pytest.mark.parametrize("tile_n", [0, 64, 128])
+@pytest.mark.parametrize("m,n,k,split", [(128, 4096, 8192, 4), (256, 4096, 8192, 2), (16, 4096, 8192, 2), (100, 136, 1024, 4),
+                                         (256, 264, 768, 2), (300, 520, 2080, 4), (64, 64, 256, 2)])
+def test_cluster_splitk_matches_workspace_splitk_bit_for_bit(ops, m, n, k, split, tile_n):
+    # split-K reduced through distributed shared memory against the workspace + reduce-kernel form:
+    # same K ranges, same order of FP32 additions, so the FP16 results are identical; ragged rows and
+    # columns, several tiles per cluster (persistent loop, slot hand-back), a split without work
+    from sm120_nvfp4_b200 import _lib
+    L = _lib.lib()
+    L.b200_nvfp4_set_tile_n(tile_n)
+    a, sfa, b, sfb = _random_case(m, n, k, 1300 + m + split)
+    da, db, dsfa, dsfb = _dev(a), _dev(b), _dev(sfa), _dev(sfb)
+    stream = torch.cuda.current_stream().cuda_stream
+    want = torch.empty((m, n), dtype=torch.float16, device="cuda")
+    ws = torch.empty(split * m * n, dtype=torch.float32, device="cuda")
+    assert L.b200_nvfp4_gemm_splitk(m, n, k, split, da.data_ptr(), db.data_ptr(), dsfa.data_ptr(), dsfb.data_ptr(),
+                                    want.data_ptr(), ws.data_ptr(), ws.numel() * 4, stream) == 0
+    for rep in range(2):
+        got = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+        assert L.b200_nvfp4_gemm_splitk_cluster(m, n, k, split, da.data_ptr(), db.data_ptr(), dsfa.data_ptr(),
+                                                dsfb.data_ptr(), got.data_ptr(), stream) == 0
+        torch.cuda.synchronize()
+        np.testing.assert_array_equal(got.cpu().numpy(), want.cpu().numpy())
+    L.b200_nvfp4_set_tile_n(0)
+    assert L.b200_nvfp4_gemm_splitk_cluster(m, n, k, 3, da.data_ptr(), db.data_ptr(), dsfa.data_ptr(), dsfb.data_ptr(),
+                                            got.data_ptr(), stream) == _lib.STATUS_INVALID_ARGUMENT
     _no_device_error()
 
 
