@@ -663,6 +663,7 @@ def moe_reading(weights: MoeWeights, tokens_per_rank: int, label: str, steps: in
     tokens_total = tokens_per_rank * world
     reading = {"label": label, "tokens_per_rank": tokens_per_rank, "tokens_total": tokens_total,
                "tokens_per_s": tokens_total / (ms * 1e-3), "ms_per_step": ms, **percentiles(per_step),
+               "per_step_ms_this_rank": [round(v, 4) for v in per_step],
                "steps": steps, "warmup": warmup, "transport": wl.transport, "experts_per_rank": weights.e_local,
                "gpu_launches_per_step": int(launches_per_step), "clocks": clocks}
     if wl.events is not None:

@@ -16,6 +16,7 @@ STATUS_SUCCESS = 0
 STATUS_INVALID_ARGUMENT = 1
 STATUS_UNSUPPORTED_DEVICE = 2
 STATUS_INSUFFICIENT_WORKSPACE = 3
+STATUS_NOT_SUPPORTED = 4
 STATUS_CUDA_ERROR = 6
 
 vp = C.c_void_p

@@ -213,13 +213,16 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
 //     need every SM pulling.
 // The override (b200_nvfp4_set_tile_n) takes 64 / 128 / 256 for single-CTA tiles and 512 for
 // the CTA-pair tile.
+constexpr int kPairTileMinRows = 160;
+
 int pick_tile(const LaunchSpec& s, const DeviceInfo& dev) {
   const long long mt = s.expected_m_tiles > 0 ? s.expected_m_tiles : 1;
   const long long splits = s.num_splits;
   auto tasks = [&](int bn) { return mt * ((s.n + bn - 1) / bn) * splits; };
-  // a pair tile is 256 rows tall: groups much shorter than that would leave half of every
-  // pair idle, and such shapes are bound by streaming the weights anyway
-  const bool tall_groups = s.avg_group_rows >= 384;
+  // a pair tile is 256 rows tall: groups of about 128 rows would leave half of every pair idle
+  // (measured on 16 k rows over N = 4096, K = 7168 / N = 7168, K = 2048: a tie at 128 rows per group,
+  // the pair tile ahead by 10 - 20 % from 192 rows on)
+  const bool tall_groups = s.avg_group_rows >= kPairTileMinRows;
   if (!s.out_f32 && splits == 1 && tall_groups &&
       ((mt + 1) / 2) * ((s.n + 255) / 256) >= dev.sm_count / 2)
     return 512;
@@ -545,7 +548,7 @@ int gemm_grouped_swiglu(void* q_out, void* q_scale, const void* x, const void* w
   // tall groups on CTA pairs, short ones on single CTAs: the rule of the plain grouped GEMM
   const int forced = env_tile_n();
   const bool pair = forced ? forced == 512
-                           : (avg >= 384 && ((est + 1) / 2) * (inter / 128) >= dev.sm_count / 2);
+                           : (avg >= kPairTileMinRows && ((est + 1) / 2) * (inter / 128) >= dev.sm_count / 2);
   return pair ? launch_instance<256, false, true, true>(s, dev, stream)
               : launch_instance<256, false, false, true>(s, dev, stream);
 }

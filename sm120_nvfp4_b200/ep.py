@@ -226,7 +226,8 @@ class ExpertParallelMoE:
             "ids": torch.empty((rows, k), **i32), "wts": torch.empty((rows, k), dtype=torch.float32, device=device),
             "gin": torch.empty((total, hidden // 2), **u8),
             "gin_s": torch.empty((self.e_local, m_pad * scale_k_padded(hidden)), **u8),
-            "gout": torch.empty((total, 2 * inter), **f16), "din": torch.empty((total, inter // 2), **u8),
+            "gout": None,    # FP16 gate/up product: only the unfused fallback needs it (allocated there)
+            "din": torch.empty((total, inter // 2), **u8),
             "din_s": torch.empty((self.e_local, m_pad * scale_k_padded(inter)), **u8),
             "dout": torch.empty((total, hidden), **f16), "pos": torch.empty((rows, k), **i32),
             "seq": torch.empty(self.e_local, **i32), "cu": torch.empty(self.e_local + 1, **i32),
@@ -277,13 +278,24 @@ class ExpertParallelMoE:
             ws["gin"].data_ptr(), ws["gin_s"].data_ptr(), ws["xq"].data_ptr(), ws["xs"].data_ptr(), ws["ids"].data_ptr(),
             ws["pos"].data_ptr(), ws["seq"].data_ptr(), ws["cu"].data_ptr(), rows, hidden, k, self.e_local, self.rank,
             ws["in_pad"], m_pad, 0, stream), "moe_count_and_gather")
-        _lib.check(L.b200_nvfp4_grouped_gemm(
-            ws["gout"].data_ptr(), ws["gin"].data_ptr(), self.gw.data_ptr(), ws["seq"].data_ptr(), ws["cu"].data_ptr(),
-            ws["gin_s"].data_ptr(), self.gws.data_ptr(), None, None, None, self.e_local, total, 2 * inter, hidden, m_pad,
-            avg, 1, None, stream), "grouped_gemm (gate/up)")
-        _lib.check(L.b200_nvfp4_moe_act_mul_and_quant(
-            ws["din"].data_ptr(), ws["din_s"].data_ptr(), ws["gout"].data_ptr(), ws["seq"].data_ptr(), ws["cu"].data_ptr(),
-            self.e_local, total, m_pad, inter, 0, stream), "moe_act_mul_and_quant")
+        # gate/up projection with SiLU * up and the quantisation in its epilogue; the two separate steps
+        # only where the fused kernel does not cover the intermediate size (same bytes either way)
+        status = L.b200_nvfp4_grouped_gemm_swiglu_quant(
+            ws["din"].data_ptr(), ws["din_s"].data_ptr(), ws["gin"].data_ptr(), self.gw.data_ptr(), ws["seq"].data_ptr(),
+            ws["cu"].data_ptr(), ws["gin_s"].data_ptr(), self.gws.data_ptr(), None, None, self.e_local, total, inter,
+            hidden, m_pad, m_pad, avg, stream)
+        if status == _lib.STATUS_NOT_SUPPORTED:
+            if ws["gout"] is None:
+                ws["gout"] = torch.empty((total, 2 * inter), dtype=torch.float16, device=device)
+            _lib.check(L.b200_nvfp4_grouped_gemm(
+                ws["gout"].data_ptr(), ws["gin"].data_ptr(), self.gw.data_ptr(), ws["seq"].data_ptr(), ws["cu"].data_ptr(),
+                ws["gin_s"].data_ptr(), self.gws.data_ptr(), None, None, None, self.e_local, total, 2 * inter, hidden,
+                m_pad, avg, 1, None, stream), "grouped_gemm (gate/up)")
+            _lib.check(L.b200_nvfp4_moe_act_mul_and_quant(
+                ws["din"].data_ptr(), ws["din_s"].data_ptr(), ws["gout"].data_ptr(), ws["seq"].data_ptr(),
+                ws["cu"].data_ptr(), self.e_local, total, m_pad, inter, 0, stream), "moe_act_mul_and_quant")
+        else:
+            _lib.check(status, "grouped_gemm_swiglu_quant")
         _lib.check(L.b200_nvfp4_grouped_gemm(
             ws["dout"].data_ptr(), ws["din"].data_ptr(), self.dw.data_ptr(), ws["seq"].data_ptr(), ws["cu"].data_ptr(),
             ws["din_s"].data_ptr(), self.dws.data_ptr(), None, None, None, self.e_local, total, hidden, inter, m_pad,
