@@ -180,7 +180,9 @@ B200_NVFP4_API int b200_nvfp4_moe_act_mul_and_quant(void* output, void* output_s
                                                     b200_stream_t stream);
 
 /* fused_moe::quantize_expert_nvfp4_async (fused_moe.hpp:35-39,
- * src/fused_moe/activation.cu:197-232): FP16 / BF16 rows -> NVFP4, expert-major. */
+ * src/fused_moe/activation.cu:197-232): FP16 / BF16 rows -> NVFP4, expert-major.
+ * input_is_bf16: 0 = FP16, 1 = BF16 (the reference's two types), 2 = FP32 rows (an addition, for
+ * packing weights from FP32 or dequantised FP8 checkpoints without an intermediate rounding). */
 B200_NVFP4_API int b200_nvfp4_moe_quantize_expert(void* output, void* output_scale,
                                                   const void* input, const void* seqlens,
                                                   const void* cu_seqlens, int num_expert_local,

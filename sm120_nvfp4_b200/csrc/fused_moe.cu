@@ -172,7 +172,7 @@ int b200_nvfp4_moe_quantize_expert(void* output, void* output_scale, const void*
                                    int input_is_bf16, int zero_scales, b200_stream_t stream) {
   return b200::moe_quantize_expert(output, output_scale, input, seqlens, cu_seqlens, nullptr,
                                    num_expert_local, total_rows, hidden_size, grouped_scale_m_pad,
-                                   input_is_bf16 != 0, zero_scales != 0,
+                                   input_is_bf16, zero_scales != 0,
                                    static_cast<cudaStream_t>(stream));
 }
 
@@ -183,7 +183,7 @@ int b200_nvfp4_moe_quantize_expert_gather(void* output, void* output_scale, cons
                                           int zero_scales, b200_stream_t stream) {
   return b200::moe_quantize_expert(output, output_scale, input, seqlens, cu_seqlens, row_map,
                                    num_expert_local, total_rows, hidden_size, grouped_scale_m_pad,
-                                   input_is_bf16 != 0, zero_scales != 0,
+                                   input_is_bf16, zero_scales != 0,
                                    static_cast<cudaStream_t>(stream));
 }
 

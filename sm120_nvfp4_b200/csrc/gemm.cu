@@ -223,9 +223,7 @@ int pick_tile(const LaunchSpec& s, const DeviceInfo& dev) {
   // (measured on 16 k rows over N = 4096, K = 7168 / N = 7168, K = 2048: a tie at 128 rows per group,
   // the pair tile ahead by 10 - 20 % from 192 rows on)
   const bool tall_groups = s.avg_group_rows >= kPairTileMinRows;
-  if (!s.out_f32 && splits == 1 && tall_groups &&
-      ((mt + 1) / 2) * ((s.n + 255) / 256) >= dev.sm_count / 2)
-    return 512;
+  if (splits == 1 && tall_groups && ((mt + 1) / 2) * ((s.n + 255) / 256) >= dev.sm_count / 2) return 512;
   if (tasks(256) >= dev.sm_count * 2 / 3) return 256;
   if (tasks(128) >= dev.sm_count * 3 / 4) return 128;
   return 64;
@@ -250,7 +248,6 @@ int launch_gemm(const LaunchSpec& s, cudaStream_t stream, int force_tile = 0) {
   if (!dev.ok) return B200_NVFP4_CUDA_ERROR;
   if (!device_supported(dev)) return B200_NVFP4_UNSUPPORTED_DEVICE;
   int tile = force_tile ? force_tile : pick_tile(s, dev);
-  if (tile == 512 && s.out_f32) tile = 256;
   if (s.cluster_split > 1 && tile > 128) tile = 128;     // the on-chip reduction is built for 64 / 128 columns
   int split = s.cluster_split > 1 ? s.cluster_split : (s.cluster_split == 1 ? pick_cluster_split(s, dev, tile) : 1);
   // A skinny problem is bound by what one thread can issue per byte of B (four MMAs and eight scale
@@ -268,7 +265,8 @@ int launch_gemm(const LaunchSpec& s, cudaStream_t stream, int force_tile = 0) {
   }
   switch (tile) {
     case 512:
-      return launch_instance<256, false, true>(s, dev, stream);
+      return s.out_f32 ? launch_instance<256, true, true>(s, dev, stream)
+                       : launch_instance<256, false, true>(s, dev, stream);
     case 256:
       return s.out_f32 ? launch_instance<256, true, false>(s, dev, stream)
                        : launch_instance<256, false, false>(s, dev, stream);

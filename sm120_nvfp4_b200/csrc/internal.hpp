@@ -50,7 +50,7 @@ int moe_act_mul_and_quant(void* output, void* output_scale, const void* gate_up,
 
 int moe_quantize_expert(void* output, void* output_scale, const void* input, const void* seqlens,
                         const void* cu_seqlens, const void* row_map, int num_expert_local,
-                        int total_rows, int hidden_size, int grouped_scale_m_pad, bool input_is_bf16,
+                        int total_rows, int hidden_size, int grouped_scale_m_pad, int input_dtype,
                         bool zero_scales, cudaStream_t stream);
 
 int moe_route(const void* topk_ids, void* topk_pos, void* seqlens, void* cu_seqlens, int num_tokens,

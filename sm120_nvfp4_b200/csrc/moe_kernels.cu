@@ -258,7 +258,7 @@ __device__ __forceinline__ void load16(const __nv_bfloat16* p, float (&v)[16]) {
   }
 }
 
-// kMode 0: silu(gate) * up from FP16 [rows, 2*width]; 1: FP16 rows; 2: BF16 rows.
+// kMode 0: silu(gate) * up from FP16 [rows, 2*width]; 1: FP16 rows; 2: BF16 rows; 3: FP32 rows.
 template <int kMode>
 __global__ void __launch_bounds__(256)
 quant_rows_kernel(uint8_t* __restrict__ output, uint8_t* __restrict__ output_scale,
@@ -294,8 +294,15 @@ quant_rows_kernel(uint8_t* __restrict__ output, uint8_t* __restrict__ output_sca
         silu_mul_block16(g, u, v);
       } else if constexpr (kMode == 1) {
         load16(static_cast<const __half*>(input) + in_row * width + kb * 16, v);
-      } else {
+      } else if constexpr (kMode == 2) {
         load16(static_cast<const __nv_bfloat16*>(input) + in_row * width + kb * 16, v);
+      } else {
+        const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(input) + in_row * width + kb * 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float4 f = src[i];
+          v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+        }
       }
       uint32_t lo, hi;
       code = quantize_block16(v, lo, hi);
@@ -576,15 +583,21 @@ int moe_act_mul_and_quant(void* output, void* output_scale, const void* gate_up,
 
 int moe_quantize_expert(void* output, void* output_scale, const void* input, const void* seqlens,
                         const void* cu_seqlens, const void* row_map, int num_expert_local,
-                        int total_rows, int hidden_size, int grouped_scale_m_pad, bool input_is_bf16,
+                        int total_rows, int hidden_size, int grouped_scale_m_pad, int input_dtype,
                         bool zero_scales, cudaStream_t stream) {
-  return input_is_bf16
-             ? launch_quant<2>(output, output_scale, input, seqlens, cu_seqlens, row_map,
-                               num_expert_local, total_rows, hidden_size, grouped_scale_m_pad,
-                               zero_scales, stream)
-             : launch_quant<1>(output, output_scale, input, seqlens, cu_seqlens, row_map,
-                               num_expert_local, total_rows, hidden_size, grouped_scale_m_pad,
-                               zero_scales, stream);
+  switch (input_dtype) {   // 0 FP16, 1 BF16, 2 FP32
+    case 0:
+      return launch_quant<1>(output, output_scale, input, seqlens, cu_seqlens, row_map, num_expert_local,
+                             total_rows, hidden_size, grouped_scale_m_pad, zero_scales, stream);
+    case 1:
+      return launch_quant<2>(output, output_scale, input, seqlens, cu_seqlens, row_map, num_expert_local,
+                             total_rows, hidden_size, grouped_scale_m_pad, zero_scales, stream);
+    case 2:
+      return launch_quant<3>(output, output_scale, input, seqlens, cu_seqlens, row_map, num_expert_local,
+                             total_rows, hidden_size, grouped_scale_m_pad, zero_scales, stream);
+    default:
+      return B200_NVFP4_INVALID_ARGUMENT;
+  }
 }
 
 // Routing only (no payload movement): seqlens / cu_seqlens / topk_pos as in

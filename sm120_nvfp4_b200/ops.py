@@ -546,19 +546,66 @@ def router_topk(logits: torch.Tensor, num_topk: int) -> Tuple[torch.Tensor, torc
     return ids, weights
 
 
-def pack_weights(weight: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """BF16 / FP16 expert weights [E, N, K] -> (packed E2M1 uint8 [E, N, K/2], UE4M3 scales uint8
-    [E, align128(N) * scale_k_padded(K)]) in the layout grouped_gemm / fused_moe expect for
-    `weight` / `weight_scale`: one UE4M3 scale = amax / 6 per 16 values of K, one 128-row-aligned
-    block-scaled region per expert. Uses the row quantiser of quantize_expert with one group per
-    expert.
+def pack_weights(weight: torch.Tensor, weight_scale: Optional[torch.Tensor] = None, *,
+                 global_scale: bool = False):
+    """Expert weights [E, N, K] from a checkpoint -> NVFP4 in the layout grouped_gemm / fused_moe expect
+    for `weight` / `weight_scale`: (packed E2M1 uint8 [E, N, K/2], UE4M3 scales uint8
+    [E, align128(N) * scale_k_padded(K)]), one UE4M3 scale = amax / 6 per 16 values of K, one
+    128-row-aligned block-scaled region per expert.
+
+    weight        BF16, FP16, FP32 or FP8 (float8_e4m3fn) values.
+    weight_scale  optional FP32 dequantisation scales of an FP8 checkpoint: [E] (per tensor) or
+                  [E, ceil(N/128), ceil(K/128)] (128 x 128 blocks); the weight used is value * scale.
+    global_scale  False: the reference's convention, a global scale of 1.0. True: a per-expert FP32 scale
+                  g = amax / (448 * 6) is divided out first, so that the block scales use UE4M3's whole
+                  range whatever the magnitude of the weights; a third tensor g [E] is returned, to be
+                  applied to the GEMM output (grouped_gemm's group_alpha / the caller's epilogue).
+
+    BF16 / FP16 inputs without scales go to the row quantiser as they are; everything else is brought to
+    FP32 first (FP8 values and the products with FP32 scales are exact or correctly rounded there) and
+    quantised from FP32.
     """
-    _check(weight.is_cuda and weight.dim() == 3 and weight.dtype in (torch.bfloat16, torch.float16) and
-           weight.is_contiguous(), "weight must be a contiguous BF16/FP16 CUDA tensor [experts, N, K]")
+    _check(weight.is_cuda and weight.dim() == 3 and weight.is_contiguous(),
+           "weight must be a contiguous CUDA tensor [experts, N, K]")
+    fp8 = getattr(torch, "float8_e4m3fn", None)
+    _check(weight.dtype in (torch.bfloat16, torch.float16, torch.float32) or (fp8 is not None and weight.dtype == fp8),
+           "weight must be BF16, FP16, FP32 or float8_e4m3fn")
     e, n, k = weight.shape
     _check(k % 32 == 0, "K must be a multiple of 32")
     dev = weight.device
+    direct = weight.dtype in (torch.bfloat16, torch.float16) and weight_scale is None and not global_scale
+    if direct:
+        w = weight
+    else:
+        w = weight.to(torch.float32)
+        if weight_scale is not None:
+            _check(weight_scale.is_cuda and weight_scale.dtype == torch.float32, "weight_scale must be FP32 on the device")
+            if weight_scale.dim() == 1:
+                _check(weight_scale.shape[0] == e, "per-tensor weight_scale must be [experts]")
+                w = w * weight_scale.view(e, 1, 1)
+            else:
+                nb, kb = (n + 127) // 128, (k + 127) // 128
+                _check(tuple(weight_scale.shape) == (e, nb, kb), "block weight_scale must be [experts, ceil(N/128), ceil(K/128)]")
+                full = weight_scale.repeat_interleave(128, dim=1)[:, :n].repeat_interleave(128, dim=2)[:, :, :k]
+                w = w * full
+    alpha = None
+    if global_scale:
+        amax = w.abs().amax(dim=(1, 2)).to(torch.float32)
+        alpha = torch.where(amax > 0, amax / (448.0 * 6.0), torch.ones_like(amax))
+        w = w / alpha.view(e, 1, 1)
+    w = w.contiguous()
     seqlens = torch.full((e,), n, dtype=torch.int32, device=dev)
     cu = torch.arange(0, (e + 1) * n, n, dtype=torch.int32, device=dev)
-    packed, scales = quantize_expert(weight.view(e * n, k), seqlens, cu, scale_m_pad=(n + 127) // 128 * 128)
-    return packed.view(e, n, k // 2), scales
+    m_pad = (n + 127) // 128 * 128
+    if w.dtype == torch.float32:
+        packed = torch.empty((e * n, k // 2), dtype=torch.uint8, device=dev)
+        scales = torch.empty((e, m_pad * scale_k_padded(k)), dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            status = _lib.lib().b200_nvfp4_moe_quantize_expert(packed.data_ptr(), scales.data_ptr(), w.data_ptr(),
+                                                               seqlens.data_ptr(), cu.data_ptr(), e, e * n, k, m_pad, 2,
+                                                               1, _stream(dev))
+        _check(status == 0, f"quantize_expert_nvfp4 launch failed: {_lib.status_string(status)}")
+    else:
+        packed, scales = quantize_expert(w.view(e * n, k), seqlens, cu, scale_m_pad=m_pad)
+    packed = packed.view(e, n, k // 2)
+    return (packed, scales, alpha) if global_scale else (packed, scales)

@@ -384,6 +384,44 @@ def test_pack_weights_matches_row_quantiser(ops):
         np.testing.assert_array_equal(scales[e].cpu().numpy()[off], sc[off])
 
 
+def test_pack_weights_from_fp32_fp8_and_with_a_global_scale(ops):
+    # the packer's other inputs: FP32 rows (quantised from FP32, compared with the oracle's FP32 row
+    # quantiser), an FP8 checkpoint with per-tensor and with 128 x 128 block scales (dequantised value
+    # by value on the host for the oracle), and the per-expert global scale g = amax / (448 * 6)
+    experts, n, k = 2, 136, 256
+    rng = np.random.default_rng(11)
+    wf = (rng.standard_normal((experts, n, k)) * 0.02).astype(np.float32)
+
+    def check(packed, scales, ref_f32):
+        for e in range(experts):
+            pk, sc = oracle.quantize_rows(ref_f32[e])
+            np.testing.assert_array_equal(packed[e].cpu().numpy(), pk)
+            nkb = k // 16
+            r = np.repeat(np.arange(n, dtype=np.int32), nkb)
+            kb = np.tile(np.arange(nkb, dtype=np.int32), n)
+            off = oracle.sf_offsets(r, kb, k)
+            np.testing.assert_array_equal(scales[e].cpu().numpy()[off], sc[off])
+
+    packed, scales = ops.pack_weights(torch.from_numpy(wf).cuda())
+    check(packed, scales, wf)
+    # FP8 checkpoint: values on the E4M3 grid, FP32 scales
+    w8 = torch.from_numpy(wf * 50).to(torch.float8_e4m3fn)
+    v8 = w8.to(torch.float32).numpy()
+    per_tensor = np.array([0.02, 0.013], np.float32)
+    packed, scales = ops.pack_weights(w8.cuda(), torch.from_numpy(per_tensor).cuda())
+    check(packed, scales, v8 * per_tensor[:, None, None])
+    blocks = (rng.random((experts, 2, 2)) * 0.02 + 0.005).astype(np.float32)
+    full = np.repeat(np.repeat(blocks, 128, axis=1)[:, :n], 128, axis=2)[:, :, :k]
+    packed, scales = ops.pack_weights(w8.cuda(), torch.from_numpy(blocks).cuda())
+    check(packed, scales, v8 * full)
+    # global scale: weights divided by g first; g * dequantised weight approximates the input
+    packed, scales, g = ops.pack_weights(torch.from_numpy(wf).cuda(), global_scale=True)
+    gh = g.cpu().numpy()
+    np.testing.assert_array_equal(gh, (np.abs(wf).max(axis=(1, 2)) / np.float32(448.0 * 6.0)).astype(np.float32))
+    check(packed, scales, (torch.from_numpy(wf) / torch.from_numpy(gh).view(experts, 1, 1)).numpy())
+    assert int(scales.max()) >= 0x70          # the block scales reach the top of UE4M3's range
+
+
 @pytest.mark.parametrize("tile_n", [0, 512])
 @pytest.mark.parametrize("counts,hidden,inter", [([0, 1, 127, 129, 300], 256, 128), ([700, 5, 64], 512, 384)])
 def test_fused_gate_up_epilogue_matches_separate_steps(ops, counts, hidden, inter, tile_n):
