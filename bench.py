@@ -350,9 +350,9 @@ def run_gemm(args, world, rank, device, peaks):
     achieved = wl.flops_rank / (mean_rank * 1e-3) / 1e12
     hbm_bound = wl.flops_rank / wl.bytes_rank < fp4_peak * 1e12 / (peaks["hbm_gbs"] * 1e9)
     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from
-    # the ncu captures summarised under profiles/ (DRAM-traffic summary of the 8192^3 case, full capture
-    # of the 4096 x 4096 x 8192 case); not captured for the other workloads
-    ncu_traffic = {"gemm8192": 268.56e6, "gemm4096": 42.3e6}.get(args.workload) if world == 1 else None
+    # the ncu captures summarised under profiles/ (time-and-DRAM summary of the 8192^3 case, full capture
+    # of the 4096 x 4096 x 8192 case, launch list of the sweep); not captured for the sharded workload
+    ncu_traffic = {"gemm8192": 262.8e6, "gemm4096": 43.7e6, "gemm_m16": 19.3e6}.get(args.workload) if world == 1 else None
     if hbm_bound:
         roof = {"bound": "hbm", "achieved": wl.bytes_rank / (mean_rank * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
                 "unit": "GB/s", "peak_source": f"{peaks['source']} copy bandwidth"}
@@ -706,8 +706,8 @@ def moe_reading(weights: MoeWeights, tokens_per_rank: int, label: str, steps: in
     return reading
 
 
-def moe_block(world, rank, device, peaks, steps: int, warmup: int):
-    weights = MoeWeights(world, rank, device)
+def moe_block(world, rank, device, peaks, steps: int, warmup: int, experts: int = 256):
+    weights = MoeWeights(world, rank, device, experts=experts)
     block = {"config": {"workload": "fused_moe_deepseek_v3_shape", "hidden": weights.h, "intermediate": weights.i,
                         "experts": weights.e, "topk": weights.k, "parallelism": f"ep{world}" if world > 1 else "single",
                         "weights": "seeded N(0, 0.02^2) quantised to NVFP4", "l2": L2_NOTE}}
@@ -725,7 +725,7 @@ def moe_block(world, rank, device, peaks, steps: int, warmup: int):
 
 def run_moe(args, world, rank, device, peaks):
     steps, warmup = min(args.steps, 50), max(3, min(args.warmup, 5))
-    block = moe_block(world, rank, device, peaks, steps, warmup)
+    block = moe_block(world, rank, device, peaks, steps, warmup, args.moe_experts)
     main = block["single"] if world == 1 else block["weak"]
     line = {
         "metric": METRIC, "value": main["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": steps,
@@ -813,6 +813,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=[None, "gemm8192", "gemm4096", "gemm_nshard", "moe",
                                                          "gemm_m16", "gemm_sweep", "grouped_c3"])
+    ap.add_argument("--moe-experts", type=int, default=256,
+                    help="experts of the MoE workload (default 256; 32 with --gpus 1 is the per-rank shape of 8-way "
+                         "expert parallelism, small enough for profiler captures)")
     ap.add_argument("--no-extras", action="store_true",
                     help="only the headline workload (no sweep / moe / sustained objects)")
     args = ap.parse_args()

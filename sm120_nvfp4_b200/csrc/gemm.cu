@@ -223,7 +223,11 @@ int pick_tile(const LaunchSpec& s, const DeviceInfo& dev) {
   // (measured on 16 k rows over N = 4096, K = 7168 / N = 7168, K = 2048: a tie at 128 rows per group,
   // the pair tile ahead by 10 - 20 % from 192 rows on)
   const bool tall_groups = s.avg_group_rows >= kPairTileMinRows;
-  if (splits == 1 && tall_groups && ((mt + 1) / 2) * ((s.n + 255) / 256) >= dev.sm_count / 2) return 512;
+  // the pair tile whenever its pairs occupy (nearly) as many SMs as single 256-column tiles would: the
+  // same SMs then work with five operand stages instead of three and two thirds of the L2 traffic
+  const long long pair_ctas = 2 * ((mt + 1) / 2) * ((s.n + 255) / 256);
+  const long long single_ctas = tasks(256) < dev.sm_count ? tasks(256) : dev.sm_count;
+  if (splits == 1 && tall_groups && pair_ctas * 20 >= single_ctas * 17) return 512;
   if (tasks(256) >= dev.sm_count * 2 / 3) return 256;
   if (tasks(128) >= dev.sm_count * 3 / 4) return 128;
   return 64;
