@@ -543,6 +543,11 @@ class MoeWorkload:
         # transport of the expert-parallel exchange: "p2p" = this library's kernels store into the
         # peers' buffers over NVLink, "nccl" = all_to_all_single
         self.transport = os.environ.get("B200_NVFP4_EP_TRANSPORT", "p2p") if w.world > 1 else "none"
+        # ordering of the two hand-offs of the p2p transport: "flags" = per-rank ready words that the
+        # consuming kernels wait for, "barrier" = two full cross-GPU barriers per layer
+        self.handoff = os.environ.get("B200_NVFP4_EP_HANDOFF", "flags")
+        # down projection in this many column blocks, the return stores of a block beside the next block
+        self.return_blocks = int(os.environ.get("B200_NVFP4_EP_RETURN_BLOCKS", "1"))
         self.layer = None
         self.events = None
         if w.world > 1:
@@ -550,7 +555,8 @@ class MoeWorkload:
             layer, err = None, None
             try:
                 layer = ExpertParallelMoE(w.gw, w.gws, w.dw, w.dws, w.e, transport=self.transport,
-                                          max_tokens=tokens, num_topk=w.k)
+                                          max_tokens=tokens, num_topk=w.k, handoff=self.handoff,
+                                          return_blocks=self.return_blocks)
             except Exception as exc:   # e.g. no symmetric memory on this box
                 if self.transport != "p2p":
                     raise
@@ -636,12 +642,14 @@ def moe_reading(weights: MoeWeights, tokens_per_rank: int, label: str, steps: in
     launches0 = _lib.launch_count()
     wl.step()
     launches_per_step = _lib.launch_count() - launches0
+    # the sampler starts (and waits for its first sample) before the warm-up: started after the
+    # barrier it would let the ranks drift apart again by the start-up time of their samplers
+    sampler = ClockSampler(torch.cuda.current_device()).start()
     for _ in range(warmup):
         wl.step()
     torch.cuda.synchronize()
     barrier(world)
     torch.cuda.synchronize()
-    sampler = ClockSampler(torch.cuda.current_device()).start()
     t_begin = time.time()
     per_step, starts = [], []
     wl.events = [] if (world > 1 and wl.transport == "p2p") else None
@@ -664,7 +672,8 @@ def moe_reading(weights: MoeWeights, tokens_per_rank: int, label: str, steps: in
     reading = {"label": label, "tokens_per_rank": tokens_per_rank, "tokens_total": tokens_total,
                "tokens_per_s": tokens_total / (ms * 1e-3), "ms_per_step": ms, **percentiles(per_step),
                "per_step_ms_this_rank": [round(v, 4) for v in per_step],
-               "steps": steps, "warmup": warmup, "transport": wl.transport, "experts_per_rank": weights.e_local,
+               "steps": steps, "warmup": warmup, "transport": wl.transport, "handoff": wl.handoff if wl.transport == "p2p" else None,
+               "return_blocks": wl.return_blocks if wl.transport == "p2p" else None, "experts_per_rank": weights.e_local,
                "gpu_launches_per_step": int(launches_per_step), "clocks": clocks}
     if wl.events is not None:
         ph = phase_means(wl.events, starts)

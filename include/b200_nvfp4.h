@@ -156,6 +156,18 @@ B200_NVFP4_API int b200_nvfp4_grouped_gemm(void* y, const void* x, const void* w
                                            int num_seq_per_group_avg, int update_tma,
                                            const float* group_alpha, b200_stream_t stream);
 
+/* b200_nvfp4_grouped_gemm restricted to the output columns [col_start, col_start + col_count) of
+ * the full [m, N] product (no counterpart in the reference): y, w and w_scale are the same whole
+ * arrays as in the full call, only that column block of y is written, with the same bits as the
+ * full call writes there. col_start is a multiple of 128; col_count a multiple of 128 unless the
+ * window ends at N. Lets a caller pipeline the consumer of y against the rest of the product. */
+B200_NVFP4_API int b200_nvfp4_grouped_gemm_columns(void* y, const void* x, const void* w,
+                                                   const void* seqlens, const void* cu_seqlens,
+                                                   const void* x_scale, const void* w_scale,
+                                                   int num_group, int m, int n, int k, int m_scale_pad,
+                                                   int num_seq_per_group_avg, const float* group_alpha,
+                                                   int col_start, int col_count, b200_stream_t stream);
+
 /* fused_moe::count_and_gather_nvfp4_async (include/sm120_nvfp4/fused_moe.hpp:12-20,
  * src/fused_moe/count_and_gather.cu:96-143). Slots inside an expert are assigned in
  * ascending flat assignment index t * num_topk + r (the reference leaves the order to
@@ -351,6 +363,46 @@ B200_NVFP4_API int b200_nvfp4_ep_return_p2p(const void* const* peer_ret, const v
  * that wait for each other on one GPU may never run at the same time. */
 B200_NVFP4_API int b200_nvfp4_ep_barrier_p2p(const void* const* peer_flags, int my_rank, int world,
                                              int epoch, long long limit_cycles, b200_stream_t stream);
+
+/* ep_reduce_return_p2p over the column window [col_start, col_start + col_count) of the rows only
+ * (multiples of 8; num_topk <= 32 unless the window is the whole row): with
+ * b200_nvfp4_grouped_gemm_columns the down projection can be computed in column blocks and the
+ * partial rows of a finished block travel to their sources on a second stream while the next block is
+ * computed. No counterpart in the reference. */
+B200_NVFP4_API int b200_nvfp4_ep_reduce_return_p2p_columns(const void* const* peer_ret,
+                                                           const void* down_output, const void* topk_pos,
+                                                           const void* topk_scale, const void* counts,
+                                                           int my_rank, int world, int slot_rows,
+                                                           int hidden_size, int num_topk, int col_start,
+                                                           int col_count, b200_stream_t stream);
+
+/* The same hand-off without a full barrier: per-rank ready words instead (no counterpart in the
+ * reference). Every rank keeps 2 * world int32 words in its mapped buffer: word s (s < world) =
+ * "source rank s has delivered its records of epoch e", word world + r = "expert rank r has delivered
+ * its partial rows of epoch e".
+ *   ep_publish_p2p        after the dispatch (slot = 0) or the return stores (slot = world) on the same
+ *                         stream: system-scope fence, then `epoch` into word slot + my_rank of every
+ *                         peer. Waits for nobody.
+ *   ep_unpack_slots_ready ep_unpack_slots whose warps take up the rows of source s once ready[s] has
+ *                         reached `epoch`: sources that have delivered are unpacked while others are
+ *                         still on their way. ready = this rank's own words [0, world).
+ *   ep_sum_p2p            the source's final step - sum of the partial rows that came back, ascending
+ *                         rank order, FP32, one rounding (b200_nvfp4_moe_reduce with unit weights over
+ *                         ret_pos [num_tokens, world]) - after every ready[r] has reached `epoch`.
+ *                         ready = this rank's own words [world, 2 * world).
+ * Every wait is bounded by limit_cycles SM clocks (0 = about one second); a word that does not
+ * arrive leaves 10 | rank << 8 (records) or 11 | rank << 8 (partial rows) in the device error word,
+ * the rows concerned are treated as empty, and the kernel returns. ready = NULL waits for nothing. */
+B200_NVFP4_API int b200_nvfp4_ep_publish_p2p(const void* const* peer_flags, int my_rank, int world, int slot,
+                                             int epoch, b200_stream_t stream);
+B200_NVFP4_API int b200_nvfp4_ep_unpack_slots_ready(void* x_packed, void* x_scale, void* topk_ids,
+                                                    void* topk_weights, const void* records,
+                                                    const void* counts, int world, int slot_rows,
+                                                    int hidden_size, int num_topk, const void* ready,
+                                                    int epoch, long long limit_cycles, b200_stream_t stream);
+B200_NVFP4_API int b200_nvfp4_ep_sum_p2p(void* output, const void* ret, const void* ret_pos, int num_tokens,
+                                         int hidden_size, int world, int out_is_bf16, const void* ready,
+                                         int epoch, long long limit_cycles, b200_stream_t stream);
 
 /* ep_return_p2p fused with the reduce step that produces `partial`: the weighted sum over a slot
  * row's local experts (b200_nvfp4_moe_reduce arithmetic, FP16 result, no shared-expert term) is

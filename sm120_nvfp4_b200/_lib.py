@@ -54,6 +54,11 @@ _SIGNATURES = {
     "b200_nvfp4_ep_dispatch_p2p": (ci, [vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, vp]),
     "b200_nvfp4_ep_unpack_slots": (ci, [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp]),
     "b200_nvfp4_ep_barrier_p2p": (ci, [vp, ci, ci, ci, C.c_longlong, vp]),
+    "b200_nvfp4_ep_reduce_return_p2p_columns": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, vp]),
+    "b200_nvfp4_grouped_gemm_columns": (ci, [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp, ci, ci, vp]),
+    "b200_nvfp4_ep_publish_p2p": (ci, [vp, ci, ci, ci, ci, vp]),
+    "b200_nvfp4_ep_unpack_slots_ready": (ci, [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, ci, C.c_longlong, vp]),
+    "b200_nvfp4_ep_sum_p2p": (ci, [vp, vp, vp, ci, ci, ci, ci, vp, ci, C.c_longlong, vp]),
     "b200_nvfp4_ep_return_p2p": (ci, [vp, vp, vp, ci, ci, ci, ci, vp]),
     "b200_nvfp4_ep_reduce_return_p2p": (ci, [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]),
     "b200_nvfp4_expert_moe": (ci, [vp] * 10 + [C.c_size_t] + [ci] * 5 + [vp]),

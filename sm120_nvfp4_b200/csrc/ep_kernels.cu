@@ -244,10 +244,36 @@ ep_dispatch_p2p_kernel(PeerPointers peer_records, PeerPointers peer_counts, int*
 
 // Slot rows -> inputs of the routed layer over all world * slot_rows rows: rows a source did not
 // fill get expert id -1 in every position, so the routing ignores them.
+// Bounded wait for one ready word (written by another GPU with a system-scope release): true once
+// *flag has reached `epoch`; after `limit` clock cycles records code | (rank << 8) and gives up.
+__device__ __forceinline__ bool wait_ready(const int* flag, int epoch, long long limit, int* error, int code, int rank) {
+  const long long start = clock64();
+  while (true) {
+    int seen;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+    if (seen - epoch >= 0) return true;
+    if (clock64() - start > limit) {
+      if (error != nullptr) atomicCAS(error, 0, code | (rank << 8));
+      return false;
+    }
+    __nanosleep(64);
+  }
+}
+
+constexpr int kDispatchNotReadyCode = 10;
+constexpr int kReturnNotReadyCode = 11;
+
+// With `ready` != nullptr a warp takes up the rows of source rank s only once ready[s] has reached
+// `epoch` (the source publishes it after its dispatch stores): rows of sources that have already
+// delivered are unpacked while others are still on their way. A source that never becomes ready
+// leaves its rows marked empty and a code in the device error word.
 __global__ void __launch_bounds__(256)
 ep_unpack_slots_kernel(uint8_t* __restrict__ x_packed, uint8_t* __restrict__ x_scale, int* __restrict__ ids,
-                       float* __restrict__ weights, const uint8_t* __restrict__ records,
-                       const int* __restrict__ counts, int world, int slot_rows, int hidden, int num_topk) {
+                       float* __restrict__ weights, const uint8_t* records, const int* counts, int world,
+                       int slot_rows, int hidden, int num_topk, const int* ready, int epoch, long long limit,
+                       int* error) {
+  // records and counts are written by other GPUs while this kernel waits: plain (coherent) loads
+  // after the acquire of the ready word, no read-only-cache path.
   const int lane = threadIdx.x & 31;
   const int nkb = hidden >> 4;
   const int kt = (nkb + 3) >> 2;
@@ -257,7 +283,13 @@ ep_unpack_slots_kernel(uint8_t* __restrict__ x_packed, uint8_t* __restrict__ x_s
   const int rows = world * slot_rows;
   for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
     const int src_rank = row / slot_rows;
-    const bool valid = row - src_rank * slot_rows < counts[src_rank];
+    bool arrived = true;
+    if (ready != nullptr) {
+      int ok = 1;
+      if (lane == 0) ok = wait_ready(ready + src_rank, epoch, limit, error, kDispatchNotReadyCode, src_rank) ? 1 : 0;
+      arrived = __shfl_sync(0xffffffffu, ok, 0) != 0;
+    }
+    const bool valid = arrived && row - src_rank * slot_rows < counts[src_rank];
     if (!valid) {
       for (int j = lane; j < num_topk; j += 32) {
         ids[static_cast<long long>(row) * num_topk + j] = -1;
@@ -350,6 +382,80 @@ ep_reduce_return_p2p_kernel(PeerPointers peer_ret, const __half* __restrict__ do
   }
 }
 
+// The same step with one warp per received row (num_topk <= 32): the lanes read the row's positions
+// and weights once, the local experts (position >= 0) are found by one ballot, and every lane then
+// walks the row's 16-byte column chunks, four chunks in flight per expert, in route order - the
+// same FMA chain per element as the kernel above, so the results are bit-identical. Empty slot rows
+// cost one comparison per warp. The loads come from local HBM, the one store per chunk goes to the
+// source rank's memory.
+__global__ void __launch_bounds__(256)
+ep_reduce_return_rows_kernel(PeerPointers peer_ret, const __half* __restrict__ down_output,
+                             const int* __restrict__ topk_pos, const float* __restrict__ topk_scale,
+                             const int* __restrict__ counts, int my_rank, int world, int slot_rows, int hidden,
+                             int num_topk, int col_start, int col_count) {
+  constexpr int kInFlight = 4;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int rows = world * slot_rows;
+  const int chunks = col_count >> 3;       // 16-byte chunks of the column window [col_start, col_start + col_count)
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
+    const int src_rank = row / slot_rows;
+    const int k = row - src_rank * slot_rows;
+    if (k >= counts[src_rank]) continue;
+    int my_pos = -1;
+    float my_wt = 0.0f;
+    if (lane < num_topk) {
+      my_pos = topk_pos[static_cast<long long>(row) * num_topk + lane];
+      my_wt = topk_scale[static_cast<long long>(row) * num_topk + lane];
+    }
+    const unsigned local = __ballot_sync(0xffffffffu, my_pos >= 0);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(peer_ret.p[src_rank]) +
+                                          (static_cast<long long>(my_rank) * slot_rows + k) * hidden + col_start);
+    for (int c0 = lane; c0 < chunks; c0 += 32 * kInFlight) {
+      float acc[kInFlight][8];
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[u][i] = 0.0f;
+      for (unsigned m = local; m != 0; m &= m - 1) {
+        const int j = __ffs(m) - 1;
+        const int drow = __shfl_sync(0xffffffffu, my_pos, j);
+        const float wt = __shfl_sync(0xffffffffu, my_wt, j);
+        const uint4* src = reinterpret_cast<const uint4*>(down_output + static_cast<long long>(drow) * hidden + col_start);
+        uint4 d[kInFlight];
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+          const int c = c0 + 32 * u;
+          d[u] = c < chunks ? src[c] : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+          const uint32_t w[4] = {d[u].x, d[u].y, d[u].z, d[u].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+            acc[u][2 * i] = __fmaf_rn(__low2float(h), wt, acc[u][2 * i]);
+            acc[u][2 * i + 1] = __fmaf_rn(__high2float(h), wt, acc[u][2 * i + 1]);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) {
+        const int c = c0 + 32 * u;
+        if (c >= chunks) continue;
+        uint4 o;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const __half2 h = __floats2half2_rn(acc[u][2 * i], acc[u][2 * i + 1]);
+          ow[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        dst[c] = o;
+      }
+    }
+  }
+}
+
 // Cross-GPU barrier of the peer-memory transport. Every rank owns `world` flag words in its
 // symmetric buffer; flag s of rank r is written by rank s only. Thread r of the one block stores
 // this call's epoch into flag `my_rank` of rank r (after a system-scope fence, so the peer stores
@@ -381,6 +487,72 @@ ep_barrier_kernel(PeerPointers peer_flags, int my_rank, int world, int epoch, lo
       __nanosleep(64);
     }
     __threadfence_system();
+  }
+}
+
+// The publishing half of the barrier alone: tells every peer that this rank's stores of the
+// kernels before it on the stream are complete (system-scope fence, then the epoch into word
+// `slot + my_rank` of every peer's flag array). Nothing waits here; the consumers do, per source.
+__global__ void __launch_bounds__(kMaxWorld)
+ep_publish_kernel(PeerPointers peer_flags, int my_rank, int world, int slot, int epoch) {
+  const int r = threadIdx.x;
+  if (r < world) {
+    __threadfence_system();
+    int* remote = reinterpret_cast<int*>(peer_flags.p[r]) + slot + my_rank;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  }
+}
+
+// Final step at the source: out[t] = sum over ranks r (ascending) of the partial row rank r stored
+// into this rank's return slots, FP32 accumulation, one rounding - b200_nvfp4_moe_reduce with unit
+// weights - after a bounded wait until every rank has published its return stores of this epoch.
+template <bool kOutBf16>
+__global__ void __launch_bounds__(256)
+ep_sum_kernel(void* __restrict__ output, const __half* ret, const int* __restrict__ ret_pos,
+              int num_tokens, int hidden, int world, const int* ready, int epoch, long long limit, int* error) {
+  if (ready != nullptr) {
+    if (threadIdx.x < world) wait_ready(ready + threadIdx.x, epoch, limit, error, kReturnNotReadyCode, threadIdx.x);
+    __syncthreads();
+  }
+  const int chunks = hidden >> 3;
+  const long long items = static_cast<long long>(num_tokens) * chunks;
+  for (long long item = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; item < items;
+       item += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int token = static_cast<int>(item / chunks);
+    const int col = static_cast<int>(item % chunks) * 8;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+    const int* pos = ret_pos + static_cast<long long>(token) * world;
+    for (int r = 0; r < world; ++r) {
+      const int row = pos[r];
+      if (row < 0) continue;
+      const uint4 d = *reinterpret_cast<const uint4*>(ret + static_cast<long long>(row) * hidden + col);
+      const uint32_t w[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+        acc[2 * i] = __fmaf_rn(__low2float(h), 1.0f, acc[2 * i]);
+        acc[2 * i + 1] = __fmaf_rn(__high2float(h), 1.0f, acc[2 * i + 1]);
+      }
+    }
+    uint4 o;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if constexpr (kOutBf16) {
+        const __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+        ow[i] = *reinterpret_cast<const uint32_t*>(&b);
+      } else {
+        const __half2 h = __floats2half2_rn(acc[2 * i], acc[2 * i + 1]);
+        ow[i] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    }
+    if constexpr (kOutBf16) {
+      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(output) + static_cast<long long>(token) * hidden + col) = o;
+    } else {
+      *reinterpret_cast<uint4*>(static_cast<__half*>(output) + static_cast<long long>(token) * hidden + col) = o;
+    }
   }
 }
 
@@ -509,6 +681,16 @@ int b200_nvfp4_ep_dispatch_p2p(const void* const* peer_records, const void* cons
 int b200_nvfp4_ep_unpack_slots(void* x_packed, void* x_scale, void* topk_ids, void* topk_weights,
                                const void* records, const void* counts, int world, int slot_rows,
                                int hidden_size, int num_topk, b200_stream_t stream) {
+  return b200_nvfp4_ep_unpack_slots_ready(x_packed, x_scale, topk_ids, topk_weights, records, counts, world,
+                                          slot_rows, hidden_size, num_topk, nullptr, 0, 0, stream);
+}
+
+int b200_nvfp4_ep_unpack_slots_ready(void* x_packed, void* x_scale, void* topk_ids, void* topk_weights,
+                                     const void* records, const void* counts, int world, int slot_rows,
+                                     int hidden_size, int num_topk, const void* ready, int epoch,
+                                     long long limit_cycles, b200_stream_t stream) {
+  if (limit_cycles < 0 || (ready != nullptr && (reinterpret_cast<uintptr_t>(ready) & 3u) != 0))
+    return B200_NVFP4_INVALID_ARGUMENT;
   if (x_packed == nullptr || x_scale == nullptr || topk_ids == nullptr || topk_weights == nullptr ||
       records == nullptr || counts == nullptr || world <= 0 || world > b200::kMaxWorld || slot_rows <= 0 ||
       hidden_size <= 0 || (hidden_size % 64) != 0 || num_topk <= 0 || !b200::aligned16(x_packed) ||
@@ -523,7 +705,8 @@ int b200_nvfp4_ep_unpack_slots(void* x_packed, void* x_scale, void* topk_ids, vo
   b200::ep_unpack_slots_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<uint8_t*>(x_packed), static_cast<uint8_t*>(x_scale), static_cast<int*>(topk_ids),
       static_cast<float*>(topk_weights), static_cast<const uint8_t*>(records), static_cast<const int*>(counts),
-      world, slot_rows, hidden_size, num_topk);
+      world, slot_rows, hidden_size, num_topk, static_cast<const int*>(ready), epoch,
+      limit_cycles > 0 ? limit_cycles : (1ll << 31), b200::device_error_word());
   b200::count_launch();
   return b200::launch_status();
 }
@@ -555,6 +738,18 @@ int b200_nvfp4_ep_return_p2p(const void* const* peer_ret, const void* partial, c
 int b200_nvfp4_ep_reduce_return_p2p(const void* const* peer_ret, const void* down_output, const void* topk_pos,
                                     const void* topk_scale, const void* counts, int my_rank, int world,
                                     int slot_rows, int hidden_size, int num_topk, b200_stream_t stream) {
+  return b200_nvfp4_ep_reduce_return_p2p_columns(peer_ret, down_output, topk_pos, topk_scale, counts, my_rank,
+                                                 world, slot_rows, hidden_size, num_topk, 0, hidden_size, stream);
+}
+
+int b200_nvfp4_ep_reduce_return_p2p_columns(const void* const* peer_ret, const void* down_output,
+                                            const void* topk_pos, const void* topk_scale, const void* counts,
+                                            int my_rank, int world, int slot_rows, int hidden_size, int num_topk,
+                                            int col_start, int col_count, b200_stream_t stream) {
+  if (col_start < 0 || col_count <= 0 || (col_start % 8) != 0 || (col_count % 8) != 0 ||
+      col_start > hidden_size - col_count || (num_topk > 32 && col_count != hidden_size)) {
+    return B200_NVFP4_INVALID_ARGUMENT;
+  }
   if (peer_ret == nullptr || down_output == nullptr || topk_pos == nullptr || topk_scale == nullptr ||
       counts == nullptr || world <= 0 || world > b200::kMaxWorld || my_rank < 0 || my_rank >= world ||
       slot_rows <= 0 || hidden_size <= 0 || (hidden_size % 8) != 0 || num_topk <= 0 ||
@@ -572,10 +767,20 @@ int b200_nvfp4_ep_reduce_return_p2p(const void* const* peer_ret, const void* dow
   long long blocks = (items + 255) / 256;
   const long long max_blocks = static_cast<long long>(dev.sm_count) * 16;
   if (blocks > max_blocks) blocks = max_blocks;
-  b200::ep_reduce_return_p2p_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      ret, static_cast<const __half*>(down_output), static_cast<const int*>(topk_pos),
-      static_cast<const float*>(topk_scale), static_cast<const int*>(counts), my_rank, world, slot_rows,
-      hidden_size, num_topk);
+  if (num_topk <= 32) {
+    long long row_blocks = (static_cast<long long>(world) * slot_rows + 7) / 8;
+    const long long max_row_blocks = static_cast<long long>(dev.sm_count) * 8;
+    if (row_blocks > max_row_blocks) row_blocks = max_row_blocks;
+    b200::ep_reduce_return_rows_kernel<<<static_cast<int>(row_blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        ret, static_cast<const __half*>(down_output), static_cast<const int*>(topk_pos),
+        static_cast<const float*>(topk_scale), static_cast<const int*>(counts), my_rank, world, slot_rows,
+        hidden_size, num_topk, col_start, col_count);
+  } else {
+    b200::ep_reduce_return_p2p_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        ret, static_cast<const __half*>(down_output), static_cast<const int*>(topk_pos),
+        static_cast<const float*>(topk_scale), static_cast<const int*>(counts), my_rank, world, slot_rows,
+        hidden_size, num_topk);
+  }
   b200::count_launch();
   return b200::launch_status();
 }
@@ -597,6 +802,49 @@ int b200_nvfp4_ep_barrier_p2p(const void* const* peer_flags, int my_rank, int wo
   const long long limit = limit_cycles > 0 ? limit_cycles : (1ll << 31);   // about a second
   b200::ep_barrier_kernel<<<1, b200::kMaxWorld, 0, static_cast<cudaStream_t>(stream)>>>(flags, my_rank, world, epoch,
                                                                                      limit, error);
+  b200::count_launch();
+  return b200::launch_status();
+}
+
+int b200_nvfp4_ep_publish_p2p(const void* const* peer_flags, int my_rank, int world, int slot, int epoch,
+                              b200_stream_t stream) {
+  if (peer_flags == nullptr || world <= 0 || world > b200::kMaxWorld || my_rank < 0 || my_rank >= world || slot < 0)
+    return B200_NVFP4_INVALID_ARGUMENT;
+  b200::PeerPointers flags{};
+  for (int r = 0; r < world; ++r) {
+    if (peer_flags[r] == nullptr || (reinterpret_cast<uintptr_t>(peer_flags[r]) & 3u) != 0)
+      return B200_NVFP4_INVALID_ARGUMENT;
+    flags.p[r] = static_cast<uint8_t*>(const_cast<void*>(peer_flags[r]));
+  }
+  b200::ep_publish_kernel<<<1, b200::kMaxWorld, 0, static_cast<cudaStream_t>(stream)>>>(flags, my_rank, world, slot, epoch);
+  b200::count_launch();
+  return b200::launch_status();
+}
+
+int b200_nvfp4_ep_sum_p2p(void* output, const void* ret, const void* ret_pos, int num_tokens, int hidden_size,
+                          int world, int out_is_bf16, const void* ready, int epoch, long long limit_cycles,
+                          b200_stream_t stream) {
+  if (output == nullptr || ret == nullptr || ret_pos == nullptr || num_tokens <= 0 || hidden_size <= 0 ||
+      (hidden_size % 8) != 0 || world <= 0 || world > b200::kMaxWorld || limit_cycles < 0 ||
+      !b200::aligned16(output) || !b200::aligned16(ret) || (ready != nullptr && (reinterpret_cast<uintptr_t>(ready) & 3u) != 0)) {
+    return B200_NVFP4_INVALID_ARGUMENT;
+  }
+  const b200::DeviceInfo& dev = b200::current_device_info();
+  if (!dev.ok) return B200_NVFP4_CUDA_ERROR;
+  const long long items = static_cast<long long>(num_tokens) * (hidden_size >> 3);
+  long long blocks = (items + 255) / 256;
+  const long long max_blocks = static_cast<long long>(dev.sm_count) * 16;
+  if (blocks > max_blocks) blocks = max_blocks;
+  const long long limit = limit_cycles > 0 ? limit_cycles : (1ll << 31);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out_is_bf16)
+    b200::ep_sum_kernel<true><<<static_cast<int>(blocks), 256, 0, s>>>(
+        output, static_cast<const __half*>(ret), static_cast<const int*>(ret_pos), num_tokens, hidden_size, world,
+        static_cast<const int*>(ready), epoch, limit, b200::device_error_word());
+  else
+    b200::ep_sum_kernel<false><<<static_cast<int>(blocks), 256, 0, s>>>(
+        output, static_cast<const __half*>(ret), static_cast<const int*>(ret_pos), num_tokens, hidden_size, world,
+        static_cast<const int*>(ready), epoch, limit, b200::device_error_word());
   b200::count_launch();
   return b200::launch_status();
 }

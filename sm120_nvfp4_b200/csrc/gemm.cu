@@ -72,6 +72,8 @@ struct LaunchSpec {
   void* q_out = nullptr;
   void* q_scale = nullptr;
   long long q_scale_group_stride = 0;
+  int out_ld = 0;                       // elements between output rows; 0 = n
+  long long sfb_atom_rows_total = 0;    // atom rows the B scale map covers; 0 = groups x rows per group
 };
 
 template <int BN, bool F32, bool kTwoCta, bool kSwiGlu = false, int kClusterSplit = 1>
@@ -111,7 +113,9 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
                          kSwiGlu ? 128 : Cfg::kBRows, kStageKBytes, CU_TENSOR_MAP_SWIZZLE_128B) ||
       !encode_tmap_sf(&tmap_sfa, s.sfa, kt, static_cast<uint64_t>(s.num_groups) * sfa_group_atom_rows,
                       Cfg::kAtomsPerStage, 1) ||
-      !encode_tmap_sf(&tmap_sfb, s.sfb, kt, static_cast<uint64_t>(b_groups) * sfb_group_atom_rows,
+      !encode_tmap_sf(&tmap_sfb, s.sfb, kt,
+                      s.sfb_atom_rows_total > 0 ? static_cast<uint64_t>(s.sfb_atom_rows_total)
+                                                : static_cast<uint64_t>(b_groups) * sfb_group_atom_rows,
                       Cfg::kAtomsPerStage, kSwiGlu ? 1 : Cfg::kSfbGroups)) {
     return B200_NVFP4_CUDA_ERROR;
   }
@@ -124,11 +128,13 @@ int launch_instance(const LaunchSpec& s, const DeviceInfo& dev, cudaStream_t str
   const long long out_rows = static_cast<long long>(s.a_rows_total) * (s.num_splits > 1 ? s.num_splits : 1);
   const bool tma_store = !kSwiGlu && BN >= 128 && s.n >= box_cols && out_rows < 0x7fffffffLL &&
                          encode_tmap_2d_out(&tmap_out, s.out, static_cast<uint64_t>(out_rows),
-                                            static_cast<uint64_t>(s.n), F32, 32, box_cols);
+                                            static_cast<uint64_t>(s.n),
+                                            static_cast<uint64_t>(s.out_ld > 0 ? s.out_ld : s.n), F32, 32, box_cols);
 
   GemmParams p;
   p.tma_store = tma_store ? 1 : 0;
   p.out_rows_per_split = s.num_splits > 1 ? s.a_rows_total : 0;
+  p.out_ld = s.out_ld > 0 ? s.out_ld : s.n;
   p.num_groups = s.num_groups;
   p.n = s.n;
   p.k = s.k;
@@ -447,7 +453,15 @@ int gemm_splitk_cluster(int m, int n, int k, int split_k, const void* a, const v
 int gemm_grouped(void* y, const void* x, const void* w, const void* seqlens,
                  const void* cu_seqlens, const void* x_scale, const void* w_scale, void* tiles,
                  void* cu_tiles, int num_group, int m, int n, int k, int m_scale_pad,
-                 int num_seq_per_group_avg, const float* group_alpha, cudaStream_t stream) {
+                 int num_seq_per_group_avg, const float* group_alpha, cudaStream_t stream,
+                 int col_start, int col_count) {
+  // Column window: the launch computes y[:, col_start : col_start + col_count) of the full
+  // [m, n] product; everything else about the call (w, w_scale, y as whole arrays) stays.
+  if (col_count == 0) col_count = n - col_start;
+  if (col_start < 0 || (col_start % 128) != 0 || col_count <= 0 || col_start > n - col_count ||
+      (col_start + col_count < n && (col_count % 128) != 0)) {
+    return B200_NVFP4_INVALID_ARGUMENT;
+  }
   if (num_group <= 0 || num_group > kMaxGroups || !valid_shape(m, n, k) || y == nullptr ||
       x == nullptr || w == nullptr || seqlens == nullptr || cu_seqlens == nullptr ||
       x_scale == nullptr || w_scale == nullptr || m_scale_pad < 128 || (m_scale_pad % 128) != 0 ||
@@ -460,19 +474,21 @@ int gemm_grouped(void* y, const void* x, const void* w, const void* seqlens,
   s.num_groups = num_group;
   s.m_uniform = 0;
   s.a_rows_total = m;
-  s.n = n;
+  s.n = col_count;
   s.k = k;
   s.a = x;
-  s.b = w;
+  s.b = static_cast<const uint8_t*>(w) + static_cast<long long>(col_start) * (k / 2);
   s.sfa = x_scale;
-  s.sfb = w_scale;
+  s.sfb = static_cast<const uint8_t*>(w_scale) + static_cast<long long>(col_start) * skp;
   s.sfa_group_stride = static_cast<long long>(m_scale_pad) * skp;
   s.sfb_group_stride = static_cast<long long>(align_up_int(n, 128)) * skp;
   s.b_group_rows = n;
-  s.b_rows_total = num_group * n;
+  s.b_rows_total = num_group * n - col_start;
+  s.sfb_atom_rows_total = static_cast<long long>(num_group) * (align_up_int(n, 128) / 128) - col_start / 128;
   s.seqlens = static_cast<const int*>(seqlens);
   s.cu_seqlens = static_cast<const int*>(cu_seqlens);
-  s.out = y;
+  s.out = static_cast<__half*>(y) + col_start;
+  s.out_ld = n;
   s.out_f32 = false;
   s.num_splits = 1;
   s.group_alpha = group_alpha;
@@ -647,7 +663,18 @@ int b200_nvfp4_grouped_gemm(void* y, const void* x, const void* w, const void* s
   (void)update_tma;
   return b200::gemm_grouped(y, x, w, seqlens, cu_seqlens, x_scale, w_scale, tiles, cu_tiles,
                             num_group, m, n, k, m_scale_pad, num_seq_per_group_avg, group_alpha,
-                            static_cast<cudaStream_t>(stream));
+                            static_cast<cudaStream_t>(stream), 0, 0);
+}
+
+int b200_nvfp4_grouped_gemm_columns(void* y, const void* x, const void* w, const void* seqlens,
+                                    const void* cu_seqlens, const void* x_scale, const void* w_scale,
+                                    int num_group, int m, int n, int k, int m_scale_pad,
+                                    int num_seq_per_group_avg, const float* group_alpha, int col_start,
+                                    int col_count, b200_stream_t stream) {
+  if (col_count <= 0) return B200_NVFP4_INVALID_ARGUMENT;
+  return b200::gemm_grouped(y, x, w, seqlens, cu_seqlens, x_scale, w_scale, nullptr, nullptr, num_group, m, n,
+                            k, m_scale_pad, num_seq_per_group_avg, group_alpha,
+                            static_cast<cudaStream_t>(stream), col_start, col_count);
 }
 
 int b200_nvfp4_device_error(int* code) {

@@ -98,6 +98,7 @@ struct GemmParams {
   int* error;                 // device word that receives a non-zero code on a timed-out wait
   int a_sub_bytes;            // shared-memory bytes of one sub-stage of A: rows in the A box x 128
   int num_stages;             // depth of the operand ring in shared memory (<= kMaxStages)
+  long long out_ld;           // elements between output rows (n, or the full width when n is a column window)
   int tma_store;              // 1: the output tensor map is valid, full 32-row slabs go out by TMA store
   int out_rows_per_split;     // rows between split-K slices in the output tensor map (M), 0 without split
   // Fused gate/up variant (kSwiGlu kernels): B holds [gate rows 0..I) ; up rows I..2I) per group, a
@@ -768,7 +769,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
         {
-          __half* dst = static_cast<__half*>(p.out) + out_row * p.n + t.nt * BN + me * W + half * HW;
+          __half* dst = static_cast<__half*>(p.out) + out_row * p.out_ld + t.nt * BN + me * W + half * HW;
           const int cbase = t.nt * BN + me * W + half * HW;
 #pragma unroll
           for (int i = 0; i < HW / 8; ++i) {
@@ -869,7 +870,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                        sf_offset(row_in_group, col >> 4, (inter + 63) >> 6)) = scale_word;
         }
       } else if constexpr (kOutF32) {
-        float* dst = static_cast<float*>(p.out) + t.split * p.out_split_stride + out_row * p.n + col0;
+        float* dst = static_cast<float*>(p.out) + t.split * p.out_split_stride + out_row * p.out_ld + col0;
         constexpr int kF32Chunks = kWarpCols / 32;
 #pragma unroll 1
         for (int ci = 0; ci < kF32Chunks; ++ci) {
@@ -896,7 +897,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       } else {
-        __half* dst = static_cast<__half*>(p.out) + out_row * p.n + col0;
+        __half* dst = static_cast<__half*>(p.out) + out_row * p.out_ld + col0;
         constexpr int kChunkCols = kWarpCols >= 64 ? 64 : kWarpCols;     // columns per pass
         constexpr int kChunks = kWarpCols / kChunkCols;
         const bool plain = !empty_split && alpha == 1.0f;   // warp-uniform: no scaling needed

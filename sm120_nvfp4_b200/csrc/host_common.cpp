@@ -83,13 +83,13 @@ bool encode_tmap_sf(CUtensorMap* map, const void* base, uint64_t kt, uint64_t at
 
 // Rank-2 tiled map over a row-major matrix of 2- or 4-byte elements (store side: no L2
 // promotion).
-bool encode_tmap_2d_out(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+bool encode_tmap_2d_out(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                         bool is_f32, uint32_t box_rows, uint32_t box_cols) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return false;
   const uint64_t elem = is_f32 ? 4 : 2;
   cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * elem};
+  cuuint64_t strides[1] = {ld * elem};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t elem_strides[2] = {1, 1};
   CUresult r = fn(map, is_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,

@@ -33,7 +33,7 @@ bool encode_tmap_2d_u8(CUtensorMap* map, const void* base, uint64_t rows, uint64
 
 // Tensor map for TMA stores of an FP16 / FP32 row-major matrix [rows, cols]: box of
 // [box_rows, box_cols] elements whose rows are 128 bytes, 128-byte swizzle.
-bool encode_tmap_2d_out(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+bool encode_tmap_2d_out(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                         bool is_f32, uint32_t box_rows, uint32_t box_cols);
 
 // Rank-3 tiled map over block-scaled scale regions: {128 32-bit words of one 512-byte atom,

@@ -30,7 +30,8 @@ int gemm_splitk_cluster(int m, int n, int k, int split_k, const void* a, const v
 int gemm_grouped(void* y, const void* x, const void* w, const void* seqlens,
                  const void* cu_seqlens, const void* x_scale, const void* w_scale, void* tiles,
                  void* cu_tiles, int num_group, int m, int n, int k, int m_scale_pad,
-                 int num_seq_per_group_avg, const float* group_alpha, cudaStream_t stream);
+                 int num_seq_per_group_avg, const float* group_alpha, cudaStream_t stream,
+                 int col_start = 0, int col_count = 0);
 
 int gemm_grouped_swiglu(void* q_out, void* q_scale, const void* x, const void* w, const void* seqlens,
                         const void* cu_seqlens, const void* x_scale, const void* w_scale, void* tiles,

@@ -26,10 +26,16 @@ read-back of the split sizes per call, as in the reference script). "p2p": no co
 and no host read-back in the data path - every rank owns slotted receive / return buffers in
 symmetric memory (torch.distributed._symmetric_memory maps them, CUDA IPC over NVLink) and the pack /
 return kernels store straight into the peer's slots (b200_nvfp4_ep_dispatch_p2p / _ep_unpack_slots
-/ _ep_reduce_return_p2p), separated by two cross-GPU barriers per layer. The barrier is this
-library's kernel (b200_nvfp4_ep_barrier_p2p): epoch flags stored into the peers, a bounded wait on
-the local ones; a rank that never arrives costs the others one time-out (about a second by
-default) and shows in the device error word (_lib.device_error()), it cannot hang them.
+/ _ep_reduce_return_p2p). The two hand-offs of a layer (records delivered, partial rows delivered)
+are ordered by per-rank ready words (handoff="flags", the default): after its stores a rank
+publishes the step's epoch into one word of every peer (b200_nvfp4_ep_publish_p2p, waits for
+nobody), and the consuming kernels wait per source - the unpack kernel takes up the rows of source
+s once s has published, so ranks that delivered early are unpacked while others are still sending,
+and the final sum waits for the partial rows (b200_nvfp4_ep_unpack_slots_ready / _ep_sum_p2p).
+handoff="barrier" separates the phases by two full cross-GPU barriers instead (this library's
+b200_nvfp4_ep_barrier_p2p: epoch flags stored into the peers, a wait on the local ones). Every wait
+is bounded: a rank that never arrives costs the others one time-out (about a second by default)
+and shows in the device error word (_lib.device_error()), it cannot hang them.
 
 The compute steps go through a small backend object so that the host logic (splits, ordering,
 the two exchanges) can be exercised on CPU ranks with a checker backend supplied by the tests;
@@ -117,6 +123,27 @@ class CudaBackend:
         return out
 
 
+# Flag words of one rank: [0, 64) the barrier's, then world "records delivered" words (by source
+# rank) and world "partial rows delivered" words (by expert rank).
+BARRIER_WORDS = 64
+FLAG_WORDS = 3 * BARRIER_WORDS
+
+
+def ready_slot(which: str, world: int) -> int:
+    return BARRIER_WORDS + (0 if which == "dispatch" else world)
+
+
+def publish_ready(peer_flag, my_rank: int, world: int, which: str, step: int, device):
+    stream = torch.cuda.current_stream(device).cuda_stream
+    _lib.check(_lib.lib().b200_nvfp4_ep_publish_p2p(peer_flag, my_rank, world, ready_slot(which, world),
+                                                    wrap_epoch(step), stream), "ep_publish_p2p")
+
+
+def wrap_epoch(step: int) -> int:
+    """The step counter as the int32 the kernels compare with wrap-around (seen - epoch >= 0)."""
+    return (step + 2 ** 31) % 2 ** 32 - 2 ** 31
+
+
 class _PeerBuffers:
     """Slotted receive / return buffers of one rank, visible to every peer (symmetric memory), and
     the flag words of this library's own cross-GPU barrier (b200_nvfp4_ep_barrier_p2p: peer stores
@@ -133,7 +160,7 @@ class _PeerBuffers:
         rec_bytes = rows * self.rb
         self.cnt_off = (rec_bytes + 255) // 256 * 256
         self.flag_off = self.cnt_off + 256
-        self.ret_off = self.flag_off + 256
+        self.ret_off = self.flag_off + 4 * FLAG_WORDS
         total = self.ret_off + rows * hidden * 2
         self.buf = symm_mem.empty(total, dtype=torch.uint8, device=device)
         group = group if group is not None else dist.group.WORLD
@@ -147,7 +174,9 @@ class _PeerBuffers:
         self.rec = self.buf[:rec_bytes].view(rows, self.rb)
         self.cnt = self.buf[self.cnt_off:self.cnt_off + 4 * world].view(torch.int32)
         self.ret = self.buf[self.ret_off:total].view(torch.float16).view(rows, hidden)
-        self.epoch = 0
+        self.flags = self.buf[self.flag_off:self.flag_off + 4 * FLAG_WORDS].view(torch.int32)
+        self.epoch = 0          # barrier epochs
+        self.step = 0           # ready-word epochs: one per layer call
         self.buf.zero_()
         # set-up only: no rank may publish an epoch before every rank has cleared its flags
         torch.cuda.synchronize(device)
@@ -158,6 +187,14 @@ class _PeerBuffers:
         stream = torch.cuda.current_stream(self.buf.device).cuda_stream
         _lib.check(_lib.lib().b200_nvfp4_ep_barrier_p2p(self.peer_flag, self.my_rank, self.world, self.epoch,
                                                         self.limit, stream), "ep_barrier_p2p")
+
+    def publish(self, which: str):
+        """Tell every peer that this rank's stores of the current step's `which` phase ("dispatch" or
+        "return"), issued before this call on the current stream, are complete."""
+        publish_ready(self.peer_flag, self.my_rank, self.world, which, self.step, self.buf.device)
+
+    def ready_ptr(self, which: str) -> int:
+        return self.flags.data_ptr() + 4 * ready_slot(which, self.world)
 
 
 class ExpertParallelMoE:
@@ -171,7 +208,8 @@ class ExpertParallelMoE:
 
     def __init__(self, gate_up_weight, gate_up_weight_scale, down_weight, down_weight_scale, num_experts_total: int,
                  group: Optional[dist.ProcessGroup] = None, backend=None, transport: str = "nccl",
-                 max_tokens: int = 0, num_topk: int = 0, emulate=None, barrier_limit_cycles: int = 0):
+                 max_tokens: int = 0, num_topk: int = 0, emulate=None, barrier_limit_cycles: int = 0,
+                 handoff: str = "flags", return_blocks: int = 1):
         self.gw, self.gws, self.dw, self.dws = gate_up_weight, gate_up_weight_scale, down_weight, down_weight_scale
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -189,7 +227,17 @@ class ExpertParallelMoE:
         self._ones = None
         if transport not in ("nccl", "p2p"):
             raise ValueError("transport must be 'nccl' or 'p2p'")
-        self.transport = transport
+        if handoff not in ("flags", "barrier"):
+            raise ValueError("handoff must be 'flags' or 'barrier'")
+        self.transport, self.handoff = transport, handoff
+        self.wait_limit = int(barrier_limit_cycles)
+        # p2p transport: the down projection in this many column blocks; the partial rows of a
+        # finished block go back to their sources on a second stream while the next one is computed
+        self.return_blocks = int(return_blocks)
+        hidden_size = gate_up_weight.shape[2] * 2
+        if self.return_blocks < 1 or hidden_size % (128 * self.return_blocks) != 0:
+            raise ValueError("return_blocks must divide the hidden size into multiples of 128 columns")
+        self._side = None
         self.peers = None
         if emulate is not None:
             self.peers = emulate[2]
@@ -234,8 +282,10 @@ class ExpertParallelMoE:
         }
         return self._ws
 
-    # The p2p layer in three phases; between them every rank passes a barrier. They are separate
-    # methods so that a single process can step several emulated ranks through them in turn.
+    # The p2p layer in three phases. With handoff="flags" a phase ends by publishing its ready word
+    # and the next one waits for the words it needs inside its first kernel; with "barrier" every
+    # rank passes a barrier between them. They are separate methods so that a single process can step
+    # several emulated ranks through them in turn.
     @torch.no_grad()
     def p2p_dispatch(self, x, topk_ids, topk_weights):
         """Phase 1: quantise this rank's tokens and store their records into the destination ranks'
@@ -254,6 +304,9 @@ class ExpertParallelMoE:
                                                 topk_ids.data_ptr(), topk_weights.data_ptr(), send_pos.data_ptr(),
                                                 send_counts.data_ptr(), send_cu.data_ptr(), self.rank, w, pb.slot_rows,
                                                 t, hidden, k, int(x.dtype == torch.bfloat16), stream), "ep_dispatch_p2p")
+        if self.handoff == "flags":
+            pb.step += 1
+            pb.publish("dispatch")
         return ret_pos
 
     @torch.no_grad()
@@ -267,9 +320,13 @@ class ExpertParallelMoE:
         stream = torch.cuda.current_stream(device).cuda_stream
         rows = w * pb.slot_rows
         ws = self._p2p_workspace(rows, hidden, k, device)
-        _lib.check(L.b200_nvfp4_ep_unpack_slots(ws["xq"].data_ptr(), ws["xs"].data_ptr(), ws["ids"].data_ptr(),
-                                                ws["wts"].data_ptr(), pb.rec.data_ptr(), pb.cnt.data_ptr(), w,
-                                                pb.slot_rows, hidden, k, stream), "ep_unpack_slots")
+        flags = self.handoff == "flags"
+        _lib.check(L.b200_nvfp4_ep_unpack_slots_ready(
+            ws["xq"].data_ptr(), ws["xs"].data_ptr(), ws["ids"].data_ptr(), ws["wts"].data_ptr(), pb.rec.data_ptr(),
+            pb.cnt.data_ptr(), w, pb.slot_rows, hidden, k, pb.ready_ptr("dispatch") if flags else None,
+            wrap_epoch(pb.step) if flags else 0, self.wait_limit, stream), "ep_unpack_slots_ready")
+        if mark is not None and flags:
+            mark("wait_records_and_unpack")
         # the routed layer stage by stage (what b200_nvfp4_fused_moe runs), with its last step - the
         # weighted sum over a token's local experts - storing straight into the source ranks' slots
         inter, total, m_pad = ws["inter"], rows * k, ws["m_pad"]
@@ -296,15 +353,48 @@ class ExpertParallelMoE:
                 ws["cu"].data_ptr(), self.e_local, total, m_pad, inter, 0, stream), "moe_act_mul_and_quant")
         else:
             _lib.check(status, "grouped_gemm_swiglu_quant")
-        _lib.check(L.b200_nvfp4_grouped_gemm(
-            ws["dout"].data_ptr(), ws["din"].data_ptr(), self.dw.data_ptr(), ws["seq"].data_ptr(), ws["cu"].data_ptr(),
-            ws["din_s"].data_ptr(), self.dws.data_ptr(), None, None, None, self.e_local, total, hidden, inter, m_pad,
-            avg, 1, None, stream), "grouped_gemm (down)")
-        if mark is not None:
-            mark("routed_layer")
-        _lib.check(L.b200_nvfp4_ep_reduce_return_p2p(pb.peer_ret, ws["dout"].data_ptr(), ws["pos"].data_ptr(),
-                                                     ws["wts"].data_ptr(), pb.cnt.data_ptr(), self.rank, w, pb.slot_rows,
-                                                     hidden, k, stream), "ep_reduce_return_p2p")
+        nb = self.return_blocks
+        if nb == 1:
+            _lib.check(L.b200_nvfp4_grouped_gemm(
+                ws["dout"].data_ptr(), ws["din"].data_ptr(), self.dw.data_ptr(), ws["seq"].data_ptr(),
+                ws["cu"].data_ptr(), ws["din_s"].data_ptr(), self.dws.data_ptr(), None, None, None, self.e_local, total,
+                hidden, inter, m_pad, avg, 1, None, stream), "grouped_gemm (down)")
+            if mark is not None:
+                mark("routed_layer")
+            _lib.check(L.b200_nvfp4_ep_reduce_return_p2p(pb.peer_ret, ws["dout"].data_ptr(), ws["pos"].data_ptr(),
+                                                         ws["wts"].data_ptr(), pb.cnt.data_ptr(), self.rank, w,
+                                                         pb.slot_rows, hidden, k, stream), "ep_reduce_return_p2p")
+        else:
+            # column blocks of the down projection on this stream; the weighted sum + return stores of
+            # block b on a second stream as soon as block b is complete, beside the GEMM of block b + 1
+            main = torch.cuda.current_stream(device)
+            if self._side is None:
+                self._side = (torch.cuda.Stream(device), [torch.cuda.Event() for _ in range(nb)])
+            side, events = self._side
+            width = hidden // nb
+
+            def reduce_return(block, on):
+                _lib.check(L.b200_nvfp4_ep_reduce_return_p2p_columns(
+                    pb.peer_ret, ws["dout"].data_ptr(), ws["pos"].data_ptr(), ws["wts"].data_ptr(), pb.cnt.data_ptr(),
+                    self.rank, w, pb.slot_rows, hidden, k, block * width, width, on.cuda_stream),
+                    "ep_reduce_return_p2p_columns")
+
+            for b in range(nb):
+                _lib.check(L.b200_nvfp4_grouped_gemm_columns(
+                    ws["dout"].data_ptr(), ws["din"].data_ptr(), self.dw.data_ptr(), ws["seq"].data_ptr(),
+                    ws["cu"].data_ptr(), ws["din_s"].data_ptr(), self.dws.data_ptr(), self.e_local, total, hidden, inter,
+                    m_pad, avg, None, b * width, width, stream), "grouped_gemm_columns (down)")
+                if b < nb - 1:
+                    events[b].record(main)
+                    side.wait_event(events[b])
+                    reduce_return(b, side)
+            if mark is not None:
+                mark("routed_layer")
+            reduce_return(nb - 1, main)
+            events[nb - 1].record(side)
+            main.wait_event(events[nb - 1])
+        if flags:
+            pb.publish("return")
         if mark is not None:
             mark("reduce_and_return")
 
@@ -312,6 +402,14 @@ class ExpertParallelMoE:
     def p2p_finish(self, ret_pos, out_bf16: bool = True):
         """Phase 3: sum the partial rows that came back, in ascending rank order."""
         t, w = ret_pos.shape
+        pb = self.peers
+        if self.handoff == "flags":
+            out = torch.empty((t, pb.hidden), dtype=torch.bfloat16 if out_bf16 else torch.float16, device=ret_pos.device)
+            stream = torch.cuda.current_stream(ret_pos.device).cuda_stream
+            _lib.check(_lib.lib().b200_nvfp4_ep_sum_p2p(out.data_ptr(), pb.ret.data_ptr(), ret_pos.data_ptr(), t,
+                                                        pb.hidden, w, int(out_bf16), pb.ready_ptr("return"),
+                                                        wrap_epoch(pb.step), self.wait_limit, stream), "ep_sum_p2p")
+            return out
         if self._ones is None or self._ones.shape != (t, w) or self._ones.device != ret_pos.device:
             self._ones = torch.ones((t, w), dtype=torch.float32, device=ret_pos.device)
         return self.backend.reduce(self.peers.ret, ret_pos, self._ones, out_bf16)
@@ -326,11 +424,13 @@ class ExpertParallelMoE:
         mark("start")
         ret_pos = self.p2p_dispatch(x, topk_ids, topk_weights)
         mark("dispatch")
-        self.peers.barrier()
-        mark("barrier_after_dispatch")
+        if self.handoff == "barrier":
+            self.peers.barrier()
+            mark("barrier_after_dispatch")
         self.p2p_compute_and_return(mark)
-        self.peers.barrier()
-        mark("barrier_after_return")
+        if self.handoff == "barrier":
+            self.peers.barrier()
+            mark("barrier_after_return")
         out = self.p2p_finish(ret_pos, out_bf16)
         mark("sum")
         return out

@@ -85,28 +85,45 @@ def test_layer_on_one_rank_matches_oracle(backend):
 class _EmulatedPeers:
     """Slotted buffers of one emulated rank; the pointer tables address every emulated rank's buffers."""
 
-    def __init__(self, rank, world, slot_rows, hidden, topk, rec, cnt, ret):
+    def __init__(self, rank, world, slot_rows, hidden, topk, rec, cnt, ret, flags):
         import ctypes
         arr = ctypes.c_void_p * world
+        self.my_rank, self.world = rank, world
         self.slot_rows, self.hidden, self.topk = slot_rows, hidden, topk
         self.peer_rec = arr(*[t.data_ptr() for t in rec])
         self.peer_cnt = arr(*[t.data_ptr() for t in cnt])
         self.peer_ret = arr(*[t.data_ptr() for t in ret])
-        self.rec, self.cnt, self.ret = rec[rank], cnt[rank], ret[rank]
+        self.peer_flag = arr(*[t.data_ptr() for t in flags])
+        self.rec, self.cnt, self.ret, self.flags = rec[rank], cnt[rank], ret[rank], flags[rank]
+        self.step = 0
 
     def barrier(self):
         pass
 
+    def publish(self, which):
+        from sm120_nvfp4_b200.ep import publish_ready
+        publish_ready(self.peer_flag, self.my_rank, self.world, which, self.step, self.flags.device)
 
+    def ready_ptr(self, which):
+        from sm120_nvfp4_b200.ep import ready_slot
+        return self.flags.data_ptr() + 4 * ready_slot(which, self.world)
+
+
+@pytest.mark.parametrize("handoff,return_blocks", [("flags", 1), ("barrier", 1), ("flags", 2)])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_peer_memory_hand_off_emulated_on_one_gpu(backend, world):
+def test_peer_memory_hand_off_emulated_on_one_gpu(backend, world, handoff, return_blocks):
     # All ranks of the peer-memory transport in one process on one GPU: every emulated rank has its
     # own slotted buffers, the pointer tables address the other ranks' buffers on the same device, and
-    # the three phases of the layer run rank after rank where the real layer has its two barriers.
+    # the three phases of the layer run rank after rank: every rank has published its ready word (or
+    # would have passed the barrier) before a kernel of the next phase looks for it, so no launch ever
+    # waits on a later one.
     # Checks the layer code and the slot addressing of dispatch / unpack / reduce-and-return for more
     # than two ranks against the oracle's per-rank composition, over two calls (slot reuse).
-    from sm120_nvfp4_b200.ep import ExpertParallelMoE, record_bytes
-    experts, hidden, inter, topk, tokens, slot = 2 * world, 128, 64, 3, 29, 32
+    from sm120_nvfp4_b200 import _lib
+    from sm120_nvfp4_b200.ep import ExpertParallelMoE, FLAG_WORDS, record_bytes
+    # return_blocks = 2: the down projection in two column blocks, the return stores of the first on a
+    # second stream beside the second block's GEMM
+    experts, hidden, inter, topk, tokens, slot = 2 * world, 128 * return_blocks, 64, 3, 29, 32
     e_local = experts // world
     gw = np.empty((experts, 2 * inter, hidden // 2), np.uint8)
     gws = np.empty((experts, oracle.scale_region_bytes(2 * inter, hidden)), np.uint8)
@@ -119,12 +136,14 @@ def test_peer_memory_hand_off_emulated_on_one_gpu(backend, world):
     rec = [torch.zeros((rows, record_bytes(hidden, topk)), dtype=torch.uint8, device="cuda") for _ in range(world)]
     cnt = [torch.zeros(world, dtype=torch.int32, device="cuda") for _ in range(world)]
     ret = [torch.zeros((rows, hidden), dtype=torch.float16, device="cuda") for _ in range(world)]
+    flags = [torch.zeros(FLAG_WORDS, dtype=torch.int32, device="cuda") for _ in range(world)]
     layers = []
     for r in range(world):
         sl = slice(r * e_local, (r + 1) * e_local)
-        peers = _EmulatedPeers(r, world, slot, hidden, topk, rec, cnt, ret)
+        peers = _EmulatedPeers(r, world, slot, hidden, topk, rec, cnt, ret, flags)
         layers.append(ExpertParallelMoE(*(torch.from_numpy(a[sl].copy()).cuda() for a in (gw, gws, dw, dws)), experts,
-                                        backend=backend, transport="p2p", emulate=(world, r, peers)))
+                                        backend=backend, transport="p2p", emulate=(world, r, peers), handoff=handoff,
+                                        barrier_limit_cycles=1 << 20, return_blocks=return_blocks))
     for call in range(2):
         inputs, ret_pos = [], []
         for r in range(world):                               # phase 1 on every rank, then the barrier
@@ -143,6 +162,73 @@ def test_peer_memory_hand_off_emulated_on_one_gpu(backend, world):
             got = out.cpu().numpy().astype(np.float32)
             frob = np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)
             assert frob < 2e-2, (call, r, frob)
+    assert _lib.device_error() == 0                          # no wait ran out
+
+
+def test_ready_word_that_never_arrives_is_reported_and_its_rows_are_left_out(backend):
+    # The ready words of the peer-memory hand-off with a source that never publishes: two ranks'
+    # slots on one GPU, only rank 0's "records delivered" word is set. The unpack kernel's wait for
+    # rank 1 gives up after its limit (about half a millisecond), marks rank 1's rows empty, leaves
+    # code 10 | 1 << 8 in the device error word and returns; rank 0's rows are unpacked. The final sum
+    # reports a missing "partial rows delivered" word the same way (code 11) and still returns.
+    from sm120_nvfp4_b200 import _lib
+    from sm120_nvfp4_b200.ep import record_bytes
+    from sm120_nvfp4_b200.ops import scale_k_padded
+    L = _lib.lib()
+    world, slot, hidden, topk = 2, 4, 128, 2
+    rows = world * slot
+    rb = record_bytes(hidden, topk)
+    g = torch.Generator().manual_seed(5)
+    rec = torch.randint(0, 256, (rows, rb), dtype=torch.uint8, generator=g)
+    rec[:, hidden // 2 + hidden // 16:hidden // 2 + hidden // 16 + 4 * topk] = torch.tensor(
+        [3, 0, 0, 0, 1, 0, 0, 0], dtype=torch.uint8)        # ids (3, 1) in every record
+    rec = rec.cuda()
+    cnt = torch.tensor([3, 2], dtype=torch.int32, device="cuda")
+    ready = torch.tensor([7, 6], dtype=torch.int32, device="cuda")       # epoch 7: rank 1 is one step behind
+    xq = torch.zeros((rows, hidden // 2), dtype=torch.uint8, device="cuda")
+    xs = torch.zeros(128 * scale_k_padded(hidden), dtype=torch.uint8, device="cuda")
+    ids = torch.zeros((rows, topk), dtype=torch.int32, device="cuda")
+    wts = torch.ones((rows, topk), dtype=torch.float32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    assert L.b200_nvfp4_ep_unpack_slots_ready(xq.data_ptr(), xs.data_ptr(), ids.data_ptr(), wts.data_ptr(),
+                                              rec.data_ptr(), cnt.data_ptr(), world, slot, hidden, topk,
+                                              ready.data_ptr(), 7, 1 << 20, stream) == _lib.STATUS_SUCCESS
+    torch.cuda.synchronize()
+    assert _lib.device_error() == (10 | (1 << 8))
+    assert _lib.device_error() == 0
+    assert ids.cpu().tolist() == [[3, 1]] * 3 + [[-1, -1]] * 5          # rank 0: 3 rows; rank 1: none taken
+    assert torch.equal(xq[:3].cpu(), rec[:3, :hidden // 2].cpu())
+    assert not wts[3:].any()
+    ready[1] = 7                                                         # rank 1 publishes: everything is taken
+    assert L.b200_nvfp4_ep_unpack_slots_ready(xq.data_ptr(), xs.data_ptr(), ids.data_ptr(), wts.data_ptr(),
+                                              rec.data_ptr(), cnt.data_ptr(), world, slot, hidden, topk,
+                                              ready.data_ptr(), 7, 1 << 20, stream) == _lib.STATUS_SUCCESS
+    torch.cuda.synchronize()
+    assert _lib.device_error() == 0
+    assert ids.cpu().tolist() == [[3, 1]] * 3 + [[-1, -1]] + [[3, 1]] * 2 + [[-1, -1]] * 2
+    # the final sum: partial rows of rank 1 not announced
+    ret = torch.ones((rows, hidden), dtype=torch.float16, device="cuda")
+    ret_pos = torch.tensor([[0, 4], [1, -1]], dtype=torch.int32, device="cuda")
+    out = torch.zeros((2, hidden), dtype=torch.float16, device="cuda")
+    ready[1] = 6
+    assert L.b200_nvfp4_ep_sum_p2p(out.data_ptr(), ret.data_ptr(), ret_pos.data_ptr(), 2, hidden, world, 0,
+                                   ready.data_ptr(), 7, 1 << 20, stream) == _lib.STATUS_SUCCESS
+    torch.cuda.synchronize()
+    assert _lib.device_error() == (11 | (1 << 8))
+    ready[1] = 7
+    assert L.b200_nvfp4_ep_sum_p2p(out.data_ptr(), ret.data_ptr(), ret_pos.data_ptr(), 2, hidden, world, 0,
+                                   ready.data_ptr(), 7, 1 << 20, stream) == _lib.STATUS_SUCCESS
+    torch.cuda.synchronize()
+    assert _lib.device_error() == 0
+    assert out.cpu().tolist() == [[2.0] * hidden, [1.0] * hidden]
+    # the publishing half: epoch into word slot + my_rank of every peer, nobody waited for
+    import ctypes
+    words = [torch.zeros(8, dtype=torch.int32, device="cuda") for _ in range(world)]
+    table = (ctypes.c_void_p * world)(*[w_.data_ptr() for w_ in words])
+    assert L.b200_nvfp4_ep_publish_p2p(table, 1, world, 4, 9, stream) == _lib.STATUS_SUCCESS
+    torch.cuda.synchronize()
+    assert all(w_.tolist() == [0, 0, 0, 0, 0, 9, 0, 0] for w_ in words)
+    assert L.b200_nvfp4_ep_publish_p2p(table, 2, world, 4, 9, stream) == _lib.STATUS_INVALID_ARGUMENT
 
 
 def test_barrier_wait_runs_out_and_reports_the_late_rank(backend):

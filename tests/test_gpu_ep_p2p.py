@@ -36,13 +36,18 @@ def _worker(rank, world, port, result_dir):
         x = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(dev)
         ids_t, w_t = torch.from_numpy(ids).to(dev), torch.from_numpy(w).to(dev)
         nccl = ExpertParallelMoE(*weights, experts)
-        p2p = ExpertParallelMoE(*weights, experts, transport="p2p", max_tokens=64, num_topk=ids.shape[1])
+        # both orderings of the hand-offs: per-rank ready words, and two full barriers per layer
+        # and the down projection in column blocks with the return stores of a block on a second stream
+        blocks = 2 if (weights[0].shape[2] * 2) % 256 == 0 else 1
+        p2p = [ExpertParallelMoE(*weights, experts, transport="p2p", max_tokens=64, num_topk=ids.shape[1], handoff=h,
+                                 return_blocks=b) for h, b in (("flags", 1), ("barrier", 1), ("flags", blocks))]
         ok = True
         for step in range(3):    # repeated calls reuse the slots
             a = nccl.forward(x, ids_t, w_t, out_bf16=False)
-            b = p2p.forward(x, ids_t, w_t, out_bf16=False)
-            torch.cuda.synchronize()
-            ok = ok and torch.equal(a, b)
+            for layer in p2p:
+                b = layer.forward(x, ids_t, w_t, out_bf16=False)
+                torch.cuda.synchronize()
+                ok = ok and torch.equal(a, b)
         want = expected_ep_output(xb, ids, w, gw, gws, dw, dws, world)
         got = a.cpu().numpy().astype(np.float32)
         ref = want.astype(np.float32)

@@ -141,3 +141,56 @@ def test_config3_dirichlet_groups(ops, with_alpha):
         check_gemm_parity(got[cu[g] + r][:, cols], ref)
     from sm120_nvfp4_b200 import _lib
     assert _lib.device_error() == 0
+
+
+@pytest.mark.parametrize("tile_n", [0, 64, 128, 256, 512])
+def test_column_windows_write_the_same_bits_as_the_full_call(ops, tile_n):
+    # b200_nvfp4_grouped_gemm_columns: the product computed block of columns by block of columns
+    # (windows of 256, 128 and a ragged last one of 264 of N = 648) against the full call - same
+    # bits inside the window, nothing written outside it; argument checks of the window.
+    from sm120_nvfp4_b200 import _lib
+    L = _lib.lib()
+    L.b200_nvfp4_set_tile_n(tile_n)
+    groups, n, k, pad = 3, 648, 256, 384
+    counts = np.array([131, 0, 300], np.int32)
+    cu = np.array([0, 131, 131, 431], np.int32)
+    rows = 440
+    x, _ = randn_quantized(rows, k, 41)
+    xs = np.zeros((groups, pad * oracle.scale_k_padded(k)), np.uint8)
+    w = np.zeros((groups, n, k // 2), np.uint8)
+    ws = np.zeros((groups, oracle.scale_region_bytes(n, k)), np.uint8)
+    for g in range(groups):
+        w[g], ws[g] = randn_quantized(n, k, 50 + g)
+        if counts[g]:
+            _, xs_g = randn_quantized(int(counts[g]), k, 60 + g)
+            xs[g, :xs_g.size] = xs_g
+    dx, dw, dxs, dws, dc, dcu = _dev(x), _dev(w), _dev(xs), _dev(ws), _dev(counts), _dev(cu)
+    alpha = torch.tensor([0.5, 2.0, 1.25], dtype=torch.float32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    full = torch.full((rows, n), 7.0, dtype=torch.float16, device="cuda")
+    assert L.b200_nvfp4_grouped_gemm(full.data_ptr(), dx.data_ptr(), dw.data_ptr(), dc.data_ptr(), dcu.data_ptr(),
+                                     dxs.data_ptr(), dws.data_ptr(), None, None, None, groups, rows, n, k, pad, 150,
+                                     1, alpha.data_ptr(), stream) == 0
+
+    def window(y, start, count):
+        return L.b200_nvfp4_grouped_gemm_columns(y.data_ptr(), dx.data_ptr(), dw.data_ptr(), dc.data_ptr(),
+                                                 dcu.data_ptr(), dxs.data_ptr(), dws.data_ptr(), groups, rows, n, k,
+                                                 pad, 150, alpha.data_ptr(), start, count, stream)
+
+    parts = torch.full((rows, n), 7.0, dtype=torch.float16, device="cuda")
+    for start, count in ((256, 128), (0, 256), (384, 264)):
+        one = torch.full((rows, n), 7.0, dtype=torch.float16, device="cuda")
+        assert window(one, start, count) == 0
+        assert window(parts, start, count) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(one[:, start:start + count], full[:, start:start + count])
+        outside = torch.ones(n, dtype=torch.bool, device="cuda")
+        outside[start:start + count] = False
+        assert (one[:, outside] == 7.0).all()
+    assert torch.equal(parts, full)
+    bad = _lib.STATUS_INVALID_ARGUMENT
+    assert window(parts, 64, 128) == bad          # start not a multiple of 128
+    assert window(parts, 0, 200) == bad           # inner window not a multiple of 128
+    assert window(parts, 640, 128) == bad         # past the last column
+    assert window(parts, 0, 0) == bad
+    assert _lib.device_error() == 0
