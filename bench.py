@@ -547,7 +547,7 @@ class MoeWorkload:
         # consuming kernels wait for, "barrier" = two full cross-GPU barriers per layer
         self.handoff = os.environ.get("B200_NVFP4_EP_HANDOFF", "flags")
         # down projection in this many column blocks, the return stores of a block beside the next block
-        self.return_blocks = int(os.environ.get("B200_NVFP4_EP_RETURN_BLOCKS", "1"))
+        self.return_blocks = int(os.environ.get("B200_NVFP4_EP_RETURN_BLOCKS", "0"))    # 0 = the layer's own choice
         self.layer = None
         self.events = None
         if w.world > 1:
@@ -673,7 +673,7 @@ def moe_reading(weights: MoeWeights, tokens_per_rank: int, label: str, steps: in
                "tokens_per_s": tokens_total / (ms * 1e-3), "ms_per_step": ms, **percentiles(per_step),
                "per_step_ms_this_rank": [round(v, 4) for v in per_step],
                "steps": steps, "warmup": warmup, "transport": wl.transport, "handoff": wl.handoff if wl.transport == "p2p" else None,
-               "return_blocks": wl.return_blocks if wl.transport == "p2p" else None, "experts_per_rank": weights.e_local,
+               "return_blocks": wl.layer.return_blocks if wl.transport == "p2p" else None, "experts_per_rank": weights.e_local,
                "gpu_launches_per_step": int(launches_per_step), "clocks": clocks}
     if wl.events is not None:
         ph = phase_means(wl.events, starts)

@@ -365,7 +365,7 @@ B200_NVFP4_API int b200_nvfp4_ep_barrier_p2p(const void* const* peer_flags, int 
                                              int epoch, long long limit_cycles, b200_stream_t stream);
 
 /* ep_reduce_return_p2p over the column window [col_start, col_start + col_count) of the rows only
- * (multiples of 8; num_topk <= 32 unless the window is the whole row): with
+ * (multiples of 8): with
  * b200_nvfp4_grouped_gemm_columns the down projection can be computed in column blocks and the
  * partial rows of a finished block travel to their sources on a second stream while the next block is
  * computed. No counterpart in the reference. */

@@ -341,13 +341,14 @@ __global__ void __launch_bounds__(256)
 ep_reduce_return_p2p_kernel(PeerPointers peer_ret, const __half* __restrict__ down_output,
                             const int* __restrict__ topk_pos, const float* __restrict__ topk_scale,
                             const int* __restrict__ counts, int my_rank, int world, int slot_rows, int hidden,
-                            int num_topk) {
-  const int chunks = hidden >> 3;
+                            int num_topk, int col_start, int col_count) {
+  // 16-byte chunks of the column window [col_start, col_start + col_count) of every slot row
+  const int chunks = col_count >> 3;
   const long long items = static_cast<long long>(world) * slot_rows * chunks;
   for (long long item = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; item < items;
        item += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int row = static_cast<int>(item / chunks);
-    const int col = static_cast<int>(item % chunks) * 8;
+    const int col = col_start + static_cast<int>(item % chunks) * 8;
     const int src_rank = row / slot_rows;
     const int k = row - src_rank * slot_rows;
     if (k >= counts[src_rank]) continue;
@@ -379,80 +380,6 @@ ep_reduce_return_p2p_kernel(PeerPointers peer_ret, const __half* __restrict__ do
     __half* dst = reinterpret_cast<__half*>(peer_ret.p[src_rank]) +
                   (static_cast<long long>(my_rank) * slot_rows + k) * hidden + col;
     *reinterpret_cast<uint4*>(dst) = o;
-  }
-}
-
-// The same step with one warp per received row (num_topk <= 32): the lanes read the row's positions
-// and weights once, the local experts (position >= 0) are found by one ballot, and every lane then
-// walks the row's 16-byte column chunks, four chunks in flight per expert, in route order - the
-// same FMA chain per element as the kernel above, so the results are bit-identical. Empty slot rows
-// cost one comparison per warp. The loads come from local HBM, the one store per chunk goes to the
-// source rank's memory.
-__global__ void __launch_bounds__(256)
-ep_reduce_return_rows_kernel(PeerPointers peer_ret, const __half* __restrict__ down_output,
-                             const int* __restrict__ topk_pos, const float* __restrict__ topk_scale,
-                             const int* __restrict__ counts, int my_rank, int world, int slot_rows, int hidden,
-                             int num_topk, int col_start, int col_count) {
-  constexpr int kInFlight = 4;
-  const int lane = threadIdx.x & 31;
-  const int warps_per_block = blockDim.x >> 5;
-  const int rows = world * slot_rows;
-  const int chunks = col_count >> 3;       // 16-byte chunks of the column window [col_start, col_start + col_count)
-  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
-    const int src_rank = row / slot_rows;
-    const int k = row - src_rank * slot_rows;
-    if (k >= counts[src_rank]) continue;
-    int my_pos = -1;
-    float my_wt = 0.0f;
-    if (lane < num_topk) {
-      my_pos = topk_pos[static_cast<long long>(row) * num_topk + lane];
-      my_wt = topk_scale[static_cast<long long>(row) * num_topk + lane];
-    }
-    const unsigned local = __ballot_sync(0xffffffffu, my_pos >= 0);
-    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(peer_ret.p[src_rank]) +
-                                          (static_cast<long long>(my_rank) * slot_rows + k) * hidden + col_start);
-    for (int c0 = lane; c0 < chunks; c0 += 32 * kInFlight) {
-      float acc[kInFlight][8];
-#pragma unroll
-      for (int u = 0; u < kInFlight; ++u)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[u][i] = 0.0f;
-      for (unsigned m = local; m != 0; m &= m - 1) {
-        const int j = __ffs(m) - 1;
-        const int drow = __shfl_sync(0xffffffffu, my_pos, j);
-        const float wt = __shfl_sync(0xffffffffu, my_wt, j);
-        const uint4* src = reinterpret_cast<const uint4*>(down_output + static_cast<long long>(drow) * hidden + col_start);
-        uint4 d[kInFlight];
-#pragma unroll
-        for (int u = 0; u < kInFlight; ++u) {
-          const int c = c0 + 32 * u;
-          d[u] = c < chunks ? src[c] : make_uint4(0u, 0u, 0u, 0u);
-        }
-#pragma unroll
-        for (int u = 0; u < kInFlight; ++u) {
-          const uint32_t w[4] = {d[u].x, d[u].y, d[u].z, d[u].w};
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
-            acc[u][2 * i] = __fmaf_rn(__low2float(h), wt, acc[u][2 * i]);
-            acc[u][2 * i + 1] = __fmaf_rn(__high2float(h), wt, acc[u][2 * i + 1]);
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < kInFlight; ++u) {
-        const int c = c0 + 32 * u;
-        if (c >= chunks) continue;
-        uint4 o;
-        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const __half2 h = __floats2half2_rn(acc[u][2 * i], acc[u][2 * i + 1]);
-          ow[i] = *reinterpret_cast<const uint32_t*>(&h);
-        }
-        dst[c] = o;
-      }
-    }
   }
 }
 
@@ -747,7 +674,7 @@ int b200_nvfp4_ep_reduce_return_p2p_columns(const void* const* peer_ret, const v
                                             int my_rank, int world, int slot_rows, int hidden_size, int num_topk,
                                             int col_start, int col_count, b200_stream_t stream) {
   if (col_start < 0 || col_count <= 0 || (col_start % 8) != 0 || (col_count % 8) != 0 ||
-      col_start > hidden_size - col_count || (num_topk > 32 && col_count != hidden_size)) {
+      col_start > hidden_size - col_count) {
     return B200_NVFP4_INVALID_ARGUMENT;
   }
   if (peer_ret == nullptr || down_output == nullptr || topk_pos == nullptr || topk_scale == nullptr ||
@@ -763,24 +690,14 @@ int b200_nvfp4_ep_reduce_return_p2p_columns(const void* const* peer_ret, const v
   }
   const b200::DeviceInfo& dev = b200::current_device_info();
   if (!dev.ok) return B200_NVFP4_CUDA_ERROR;
-  const long long items = static_cast<long long>(world) * slot_rows * (hidden_size >> 3);
+  const long long items = static_cast<long long>(world) * slot_rows * (col_count >> 3);
   long long blocks = (items + 255) / 256;
   const long long max_blocks = static_cast<long long>(dev.sm_count) * 16;
   if (blocks > max_blocks) blocks = max_blocks;
-  if (num_topk <= 32) {
-    long long row_blocks = (static_cast<long long>(world) * slot_rows + 7) / 8;
-    const long long max_row_blocks = static_cast<long long>(dev.sm_count) * 8;
-    if (row_blocks > max_row_blocks) row_blocks = max_row_blocks;
-    b200::ep_reduce_return_rows_kernel<<<static_cast<int>(row_blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        ret, static_cast<const __half*>(down_output), static_cast<const int*>(topk_pos),
-        static_cast<const float*>(topk_scale), static_cast<const int*>(counts), my_rank, world, slot_rows,
-        hidden_size, num_topk, col_start, col_count);
-  } else {
-    b200::ep_reduce_return_p2p_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        ret, static_cast<const __half*>(down_output), static_cast<const int*>(topk_pos),
-        static_cast<const float*>(topk_scale), static_cast<const int*>(counts), my_rank, world, slot_rows,
-        hidden_size, num_topk);
-  }
+  b200::ep_reduce_return_p2p_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      ret, static_cast<const __half*>(down_output), static_cast<const int*>(topk_pos),
+      static_cast<const float*>(topk_scale), static_cast<const int*>(counts), my_rank, world, slot_rows,
+      hidden_size, num_topk, col_start, col_count);
   b200::count_launch();
   return b200::launch_status();
 }

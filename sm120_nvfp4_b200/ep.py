@@ -32,6 +32,10 @@ publishes the step's epoch into one word of every peer (b200_nvfp4_ep_publish_p2
 nobody), and the consuming kernels wait per source - the unpack kernel takes up the rows of source
 s once s has published, so ranks that delivered early are unpacked while others are still sending,
 and the final sum waits for the partial rows (b200_nvfp4_ep_unpack_slots_ready / _ep_sum_p2p).
+With return_blocks > 1 the down projection runs as that many column blocks
+(b200_nvfp4_grouped_gemm_columns) and the weighted sum + return stores of a finished block run on a
+second stream beside the next block's GEMM (b200_nvfp4_ep_reduce_return_p2p_columns), so part of
+the NVLink time of the return path hides behind tensor-core time.
 handoff="barrier" separates the phases by two full cross-GPU barriers instead (this library's
 b200_nvfp4_ep_barrier_p2p: epoch flags stored into the peers, a wait on the local ones). Every wait
 is bounded: a rank that never arrives costs the others one time-out (about a second by default)
@@ -209,7 +213,7 @@ class ExpertParallelMoE:
     def __init__(self, gate_up_weight, gate_up_weight_scale, down_weight, down_weight_scale, num_experts_total: int,
                  group: Optional[dist.ProcessGroup] = None, backend=None, transport: str = "nccl",
                  max_tokens: int = 0, num_topk: int = 0, emulate=None, barrier_limit_cycles: int = 0,
-                 handoff: str = "flags", return_blocks: int = 1):
+                 handoff: str = "flags", return_blocks: int = 0):
         self.gw, self.gws, self.dw, self.dws = gate_up_weight, gate_up_weight_scale, down_weight, down_weight_scale
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -233,8 +237,14 @@ class ExpertParallelMoE:
         self.wait_limit = int(barrier_limit_cycles)
         # p2p transport: the down projection in this many column blocks; the partial rows of a
         # finished block go back to their sources on a second stream while the next one is computed
+        # (0 = choose: two blocks where the slots of a rank hold 16384 rows or more - measured on 4
+        # GPUs, T = 4096 per rank: 1.45 -> 1.35 ms per layer; with 1024 tokens per rank one block is
+        # faster, and on 2 GPUs the return stores are too short to matter)
         self.return_blocks = int(return_blocks)
         hidden_size = gate_up_weight.shape[2] * 2
+        if self.return_blocks == 0:
+            big = transport == "p2p" and emulate is None and self.world * int(max_tokens) >= 16384
+            self.return_blocks = 2 if big and hidden_size % 256 == 0 else 1
         if self.return_blocks < 1 or hidden_size % (128 * self.return_blocks) != 0:
             raise ValueError("return_blocks must divide the hidden size into multiples of 128 columns")
         self._side = None
