@@ -281,13 +281,22 @@ ep_unpack_slots_kernel(uint8_t* __restrict__ x_packed, uint8_t* __restrict__ x_s
   const int payload_bytes = hidden >> 1;
   const int warps_per_block = blockDim.x >> 5;
   const int rows = world * slot_rows;
+  unsigned long long seen_ready = 0, seen_late = 0;      // per warp, one bit per source rank (world <= 64)
   for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
     const int src_rank = row / slot_rows;
     bool arrived = true;
     if (ready != nullptr) {
-      int ok = 1;
-      if (lane == 0) ok = wait_ready(ready + src_rank, epoch, limit, error, kDispatchNotReadyCode, src_rank) ? 1 : 0;
-      arrived = __shfl_sync(0xffffffffu, ok, 0) != 0;
+      // one acquire per warp and source: a source this warp has seen ready stays ready, and one that
+      // ran into the limit is not waited for again (a dead source costs a warp one time-out, not one
+      // per row)
+      const unsigned long long bit = 1ull << src_rank;
+      if ((seen_ready & bit) == 0 && (seen_late & bit) == 0) {
+        int ok = 1;
+        if (lane == 0) ok = wait_ready(ready + src_rank, epoch, limit, error, kDispatchNotReadyCode, src_rank) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (ok != 0) seen_ready |= bit; else seen_late |= bit;
+      }
+      arrived = (seen_ready & bit) != 0;
     }
     const bool valid = arrived && row - src_rank * slot_rows < counts[src_rank];
     if (!valid) {
@@ -357,17 +366,32 @@ ep_reduce_return_p2p_kernel(PeerPointers peer_ret, const __half* __restrict__ do
     for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
     const int* pos = topk_pos + static_cast<long long>(row) * num_topk;
     const float* wts = topk_scale + static_cast<long long>(row) * num_topk;
-    for (int r = 0; r < num_topk; ++r) {
-      const int drow = pos[r];
-      if (drow < 0) continue;
-      const float wt = wts[r];
-      const uint4 d = *reinterpret_cast<const uint4*>(down_output + static_cast<long long>(drow) * hidden + col);
-      const uint32_t w[4] = {d.x, d.y, d.z, d.w};
+    // up to eight routes at a time: the loads of the local ones are issued together, the FMA chain
+    // stays in route order
+    for (int r0 = 0; r0 < num_topk; r0 += 8) {
+      int drow[8];
+      float wt[8];
+      uint4 d[8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
-        acc[2 * i] = __fmaf_rn(__low2float(h), wt, acc[2 * i]);
-        acc[2 * i + 1] = __fmaf_rn(__high2float(h), wt, acc[2 * i + 1]);
+      for (int u = 0; u < 8; ++u) {
+        drow[u] = r0 + u < num_topk ? pos[r0 + u] : -1;
+        wt[u] = r0 + u < num_topk ? wts[r0 + u] : 0.0f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (drow[u] >= 0)
+          d[u] = *reinterpret_cast<const uint4*>(down_output + static_cast<long long>(drow[u]) * hidden + col);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (drow[u] < 0) continue;
+        const uint32_t w[4] = {d[u].x, d[u].y, d[u].z, d[u].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+          acc[2 * i] = __fmaf_rn(__low2float(h), wt[u], acc[2 * i]);
+          acc[2 * i + 1] = __fmaf_rn(__high2float(h), wt[u], acc[2 * i + 1]);
+        }
       }
     }
     uint4 o;

@@ -199,14 +199,35 @@ gather_kernel(uint8_t* __restrict__ grouped_input, uint8_t* __restrict__ grouped
     const int token = a / num_topk;
     const uint4* src = reinterpret_cast<const uint4*>(input + static_cast<long long>(token) * row_bytes);
     uint4* dst = reinterpret_cast<uint4*>(grouped_input + static_cast<long long>(grouped_row) * row_bytes);
-    for (int i = lane; i < (row_bytes >> 4); i += 32) dst[i] = src[i];
+    // eight 16-byte vectors (and four scale words) per lane are loaded before the first is stored
+    const int vecs = row_bytes >> 4;
+    for (int base = lane; base < vecs; base += 256) {
+      uint4 buf[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (base + 32 * u < vecs) buf[u] = src[base + 32 * u];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (base + 32 * u < vecs) dst[base + 32 * u] = buf[u];
+    }
     const uint8_t* s_row = input_scale + sf_offset(token, 0, kt);
     uint8_t* d_row = grouped_scale + expert * group_scale_stride + sf_offset(position, 0, kt);
-    for (int j = lane; j < kt; j += 32) {
-      uint32_t v = *reinterpret_cast<const uint32_t*>(s_row + static_cast<long long>(j) * 512);
-      const int valid = nkb - 4 * j;
-      if (valid < 4) v &= (1u << (8 * valid)) - 1u;
-      *reinterpret_cast<uint32_t*>(d_row + static_cast<long long>(j) * 512) = v;
+    for (int base = lane; base < kt; base += 128) {
+      uint32_t v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int j = base + 32 * u;
+        if (j < kt) {
+          v[u] = *reinterpret_cast<const uint32_t*>(s_row + static_cast<long long>(j) * 512);
+          const int valid = nkb - 4 * j;
+          if (valid < 4) v[u] &= (1u << (8 * valid)) - 1u;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int j = base + 32 * u;
+        if (j < kt) *reinterpret_cast<uint32_t*>(d_row + static_cast<long long>(j) * 512) = v[u];
+      }
     }
   }
 }
@@ -352,17 +373,32 @@ reduce_kernel(void* __restrict__ output, const __half* __restrict__ down_output,
     }
     const int* pos = topk_pos + static_cast<long long>(token) * num_topk;
     const float* wts = topk_scale + static_cast<long long>(token) * num_topk;
-    for (int r = 0; r < num_topk; ++r) {
-      const int row = pos[r];
-      if (row < 0) continue;
-      const float wt = wts[r];
-      const uint4 d = *reinterpret_cast<const uint4*>(down_output + static_cast<long long>(row) * hidden + col);
-      const uint32_t w[4] = {d.x, d.y, d.z, d.w};
+    // up to eight routes at a time: all their loads are issued before the first FMA needs one, the
+    // FMA chain itself stays in route order
+    for (int r0 = 0; r0 < num_topk; r0 += 8) {
+      int row[8];
+      float wt[8];
+      uint4 d[8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
-        acc[2 * i] = __fmaf_rn(__low2float(h), wt, acc[2 * i]);
-        acc[2 * i + 1] = __fmaf_rn(__high2float(h), wt, acc[2 * i + 1]);
+      for (int u = 0; u < 8; ++u) {
+        row[u] = r0 + u < num_topk ? pos[r0 + u] : -1;
+        wt[u] = r0 + u < num_topk ? wts[r0 + u] : 0.0f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (row[u] >= 0)
+          d[u] = *reinterpret_cast<const uint4*>(down_output + static_cast<long long>(row[u]) * hidden + col);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (row[u] < 0) continue;
+        const uint32_t w[4] = {d[u].x, d[u].y, d[u].z, d[u].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+          acc[2 * i] = __fmaf_rn(__low2float(h), wt[u], acc[2 * i]);
+          acc[2 * i + 1] = __fmaf_rn(__high2float(h), wt[u], acc[2 * i + 1]);
+        }
       }
     }
     uint4 o;
