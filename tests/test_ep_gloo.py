@@ -212,3 +212,31 @@ def test_a_rank_that_leaves_between_steps_ends_the_next_exchange_with_an_error(t
     mp.spawn(_leaving_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
     assert (tmp_path / "rank1.txt").read_text() == "left"
     assert (tmp_path / "rank0.txt").read_text().startswith("raised")
+
+
+def test_layer_options_are_checked_on_the_host():
+    # Constructor checks of the expert-parallel layer that need no device: transport, hand-off and
+    # column-block arguments, the expert split, and the epoch arithmetic of the ready words.
+    from sm120_nvfp4_b200.ep import BARRIER_WORDS, FLAG_WORDS, ExpertParallelMoE, ready_slot, wrap_epoch
+    hidden, inter, experts = 256, 64, 2
+    gw = torch.zeros((experts, 2 * inter, hidden // 2), dtype=torch.uint8)
+    gws = torch.zeros((experts, 1), dtype=torch.uint8)
+    dw = torch.zeros((experts, hidden, inter // 2), dtype=torch.uint8)
+    dws = torch.zeros((experts, 1), dtype=torch.uint8)
+    backend = OracleBackend()
+    layer = ExpertParallelMoE(gw, gws, dw, dws, experts, backend=backend)
+    assert layer.world == 1 and layer.return_blocks == 1 and layer.handoff == "flags"
+    assert ExpertParallelMoE(gw, gws, dw, dws, experts, backend=backend, return_blocks=2).return_blocks == 2
+    for bad in (dict(transport="rdma"), dict(handoff="events"), dict(return_blocks=3), dict(return_blocks=-1)):
+        with pytest.raises(ValueError):
+            ExpertParallelMoE(gw, gws, dw, dws, experts, backend=backend, **bad)
+    with pytest.raises(ValueError):
+        ExpertParallelMoE(gw, gws, dw, dws, experts + 1, backend=backend)       # experts do not split over the ranks
+    with pytest.raises(ValueError):
+        ExpertParallelMoE(gw, gws, dw, dws, experts, backend=backend, transport="p2p")   # needs max_tokens, num_topk
+    # ready words: after the barrier's words, `world` per kind, inside the flag area up to 64 ranks
+    assert ready_slot("dispatch", 8) == BARRIER_WORDS and ready_slot("return", 8) == BARRIER_WORDS + 8
+    assert ready_slot("return", 64) + 64 <= FLAG_WORDS
+    # epochs are compared as signed 32-bit differences, so the step counter may wrap
+    assert wrap_epoch(5) == 5 and wrap_epoch(2 ** 31 - 1) == 2 ** 31 - 1
+    assert wrap_epoch(2 ** 31) == -2 ** 31 and wrap_epoch(2 ** 32 + 3) == 3
