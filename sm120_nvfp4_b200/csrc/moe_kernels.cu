@@ -373,32 +373,17 @@ reduce_kernel(void* __restrict__ output, const __half* __restrict__ down_output,
     }
     const int* pos = topk_pos + static_cast<long long>(token) * num_topk;
     const float* wts = topk_scale + static_cast<long long>(token) * num_topk;
-    // up to eight routes at a time: all their loads are issued before the first FMA needs one, the
-    // FMA chain itself stays in route order
-    for (int r0 = 0; r0 < num_topk; r0 += 8) {
-      int row[8];
-      float wt[8];
-      uint4 d[8];
+    for (int r = 0; r < num_topk; ++r) {
+      const int row = pos[r];
+      if (row < 0) continue;
+      const float wt = wts[r];
+      const uint4 d = *reinterpret_cast<const uint4*>(down_output + static_cast<long long>(row) * hidden + col);
+      const uint32_t w[4] = {d.x, d.y, d.z, d.w};
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        row[u] = r0 + u < num_topk ? pos[r0 + u] : -1;
-        wt[u] = r0 + u < num_topk ? wts[r0 + u] : 0.0f;
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        if (row[u] >= 0)
-          d[u] = *reinterpret_cast<const uint4*>(down_output + static_cast<long long>(row[u]) * hidden + col);
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        if (row[u] < 0) continue;
-        const uint32_t w[4] = {d[u].x, d[u].y, d[u].z, d[u].w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
-          acc[2 * i] = __fmaf_rn(__low2float(h), wt[u], acc[2 * i]);
-          acc[2 * i + 1] = __fmaf_rn(__high2float(h), wt[u], acc[2 * i + 1]);
-        }
+      for (int i = 0; i < 4; ++i) {
+        const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+        acc[2 * i] = __fmaf_rn(__low2float(h), wt, acc[2 * i]);
+        acc[2 * i + 1] = __fmaf_rn(__high2float(h), wt, acc[2 * i + 1]);
       }
     }
     uint4 o;
