@@ -39,7 +39,9 @@ the NVLink time of the return path hides behind tensor-core time.
 handoff="barrier" separates the phases by two full cross-GPU barriers instead (this library's
 b200_nvfp4_ep_barrier_p2p: epoch flags stored into the peers, a wait on the local ones). Every wait
 is bounded: a rank that never arrives costs the others one time-out (about a second by default)
-and shows in the device error word (_lib.device_error()), it cannot hang them.
+and shows in the device error word (_lib.device_error()), it cannot hang them. A layer whose call
+raised or timed out on some rank is out of step with its peers (its step counter no longer matches
+theirs): build a new one before the next call.
 
 The compute steps go through a small backend object so that the host logic (splits, ordering,
 the two exchanges) can be exercised on CPU ranks with a checker backend supplied by the tests;
