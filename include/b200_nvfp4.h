@@ -427,6 +427,25 @@ B200_NVFP4_API int b200_nvfp4_device_error(int* code);
  * value. */
 B200_NVFP4_API int b200_nvfp4_set_tile_n(int tile_n);
 
+/* Shape-keyed tile table (no counterpart in the reference's ABI; its RTX 5090 tuning is compiled
+ * in). An entry fixes the tile shape - the values of b200_nvfp4_set_tile_n - for exactly one
+ * problem: `groups` problems of `rows` x n x k for the dense / batched entry points (grouped = 0),
+ * or a grouped call over `groups` groups and `rows` rows in total (grouped = 1); out_f32 selects the
+ * FP32-output entry points. tile_n = 0 removes the entry. The built-in rules apply to every problem
+ * without an entry; the split-K entry points, the dispatcher's M = 128 / 256 paths and the fused
+ * gate/up GEMM never consult the table (their tiles are part of their arithmetic).
+ * sm120_nvfp4_b200.ops.autotune_gemm / autotune_grouped_gemm time the candidates on the device
+ * and install the fastest. tune_get returns the entry's tile or 0. Thread-safe. */
+B200_NVFP4_API int b200_nvfp4_tune_set(int groups, int rows, int n, int k, int out_f32, int grouped,
+                                       int tile_n);
+B200_NVFP4_API int b200_nvfp4_tune_get(int groups, int rows, int n, int k, int out_f32, int grouped);
+B200_NVFP4_API void b200_nvfp4_tune_clear(void);
+
+/* Tile of the most recent GEMM launch of this process (any entry point): the b200_nvfp4_set_tile_n
+ * value in the low 16 bits, the number of K ranges reduced inside a cluster (1 = none) above them.
+ * For tests of the tile rules and of the table. No counterpart in the reference. */
+B200_NVFP4_API int b200_nvfp4_last_launch_tile(void);
+
 /* out_f32[i] = silu(in_f16[i]) = x / (1 + exp(-x)) exactly as b200_nvfp4_moe_act_mul_and_quant and
  * the fused gate/up epilogue evaluate it (the reference's silu(), src/fused_moe/activation.cu:17-19,
  * with this library's fixed-sequence exp): for tests that compare every FP16 input with the CPU

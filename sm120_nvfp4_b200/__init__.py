@@ -11,9 +11,9 @@ include/b200_nvfp4.h on torch's current stream. torch is used for memory and str
 """
 from __future__ import annotations
 
-from .ops import (HostGemm, cute_gemm, cutlass_gemm, expert_moe, expert_moe_workspace_bytes, fused_moe, gemm,
-                  grouped_gemm, pack_weights, quantize_expert, router_topk, scale_a_elements, scale_b_elements,
-                  scale_k_padded)
+from .ops import (HostGemm, autotune_gemm, autotune_grouped_gemm, clear_tuned_tiles, cute_gemm, cutlass_gemm,
+                  expert_moe, expert_moe_workspace_bytes, fused_moe, gemm, grouped_gemm, pack_weights,
+                  quantize_expert, router_topk, scale_a_elements, scale_b_elements, scale_k_padded, tuned_tile)
 
 __all__ = [
     "expert_moe",
@@ -32,4 +32,9 @@ __all__ = [
     "pack_weights",
     # host-memory operands, copies overlapped with the arithmetic
     "HostGemm",
+    # shape-keyed tile table
+    "autotune_gemm",
+    "autotune_grouped_gemm",
+    "tuned_tile",
+    "clear_tuned_tiles",
 ]

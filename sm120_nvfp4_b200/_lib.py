@@ -64,6 +64,10 @@ _SIGNATURES = {
     "b200_nvfp4_expert_moe": (ci, [vp] * 10 + [C.c_size_t] + [ci] * 5 + [vp]),
     "b200_nvfp4_device_error": (ci, [C.POINTER(ci)]),
     "b200_nvfp4_set_tile_n": (ci, [ci]),
+    "b200_nvfp4_tune_set": (ci, [ci, ci, ci, ci, ci, ci, ci]),
+    "b200_nvfp4_tune_get": (ci, [ci, ci, ci, ci, ci, ci]),
+    "b200_nvfp4_tune_clear": (None, []),
+    "b200_nvfp4_last_launch_tile": (ci, []),
     "b200_nvfp4_set_fused_gate_up": (ci, [ci]),
     "b200_nvfp4_silu_f16": (ci, [vp, vp, ci, vp]),
     "b200_nvfp4_set_wait_limit": (ci, [C.c_longlong, ci]),

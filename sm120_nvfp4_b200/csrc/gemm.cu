@@ -5,6 +5,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <unordered_map>
 
 #include <cuda_fp16.h>
 
@@ -233,7 +234,11 @@ int pick_tile(const LaunchSpec& s, const DeviceInfo& dev) {
   // same SMs then work with five operand stages instead of three and two thirds of the L2 traffic
   const long long pair_ctas = 2 * ((mt + 1) / 2) * ((s.n + 255) / 256);
   const long long single_ctas = tasks(256) < dev.sm_count ? tasks(256) : dev.sm_count;
-  if (splits == 1 && tall_groups && pair_ctas * 20 >= single_ctas * 17) return 512;
+  // ... unless a single dense problem is so small that its pairs cover at most half of the SMs: narrower
+  // single-CTA tiles then put more SMs to work (tuner, N = 4096, K = 8192, back to back: M = 256 13.9
+  // against 17.2 us, M = 512 16.5 against 18.5; from M = 1024 on the pair tile wins)
+  const bool small_dense = s.seqlens == nullptr && s.num_groups == 1 && pair_ctas * 2 <= dev.sm_count;
+  if (splits == 1 && tall_groups && !small_dense && pair_ctas * 20 >= single_ctas * 17) return 512;
   if (tasks(256) >= dev.sm_count * 2 / 3) return 256;
   if (tasks(128) >= dev.sm_count * 3 / 4) return 128;
   return 64;
@@ -253,10 +258,45 @@ int pick_cluster_split(const LaunchSpec& s, const DeviceInfo& dev, int tile) {
   return 1;
 }
 
+// Shape-keyed tile table (b200_nvfp4_tune_set): an entry replaces pick_tile's choice for exactly that
+// problem. Key: groups, rows (per problem for dense / batched calls, in total for grouped ones), N,
+// K, output type, and whether the row counts come from the device (grouped).
+struct TuneKey {
+  int groups, rows, n, k, flags;
+  bool operator==(const TuneKey& o) const {
+    return groups == o.groups && rows == o.rows && n == o.n && k == o.k && flags == o.flags;
+  }
+};
+struct TuneKeyHash {
+  size_t operator()(const TuneKey& key) const {
+    size_t h = 1469598103934665603ull;
+    for (int v : {key.groups, key.rows, key.n, key.k, key.flags}) h = (h ^ static_cast<size_t>(v)) * 1099511628211ull;
+    return h;
+  }
+};
+std::mutex g_tune_mutex;
+std::unordered_map<TuneKey, int, TuneKeyHash> g_tune_table;
+std::atomic<int> g_tune_entries{0};
+std::atomic<int> g_last_tile{0};      // tile | cluster split << 16 of the most recent launch_gemm
+
+TuneKey tune_key(int groups, int rows, int n, int k, bool out_f32, bool grouped) {
+  return TuneKey{groups, rows, n, k, (out_f32 ? 1 : 0) | (grouped ? 2 : 0)};
+}
+
+int tuned_tile(const LaunchSpec& s) {
+  if (g_tune_entries.load(std::memory_order_acquire) == 0 || s.swiglu_inter != 0 || s.num_splits != 1) return 0;
+  const bool grouped = s.seqlens != nullptr;
+  const TuneKey key = tune_key(s.num_groups, grouped ? s.a_rows_total : s.m_uniform, s.n, s.k, s.out_f32, grouped);
+  std::lock_guard<std::mutex> lock(g_tune_mutex);
+  auto it = g_tune_table.find(key);
+  return it == g_tune_table.end() ? 0 : it->second;
+}
+
 int launch_gemm(const LaunchSpec& s, cudaStream_t stream, int force_tile = 0) {
   const DeviceInfo& dev = current_device_info();
   if (!dev.ok) return B200_NVFP4_CUDA_ERROR;
   if (!device_supported(dev)) return B200_NVFP4_UNSUPPORTED_DEVICE;
+  if (force_tile == 0 && s.cluster_split <= 1) force_tile = tuned_tile(s);
   int tile = force_tile ? force_tile : pick_tile(s, dev);
   if (s.cluster_split > 1 && tile > 128) tile = 128;     // the on-chip reduction is built for 64 / 128 columns
   int split = s.cluster_split > 1 ? s.cluster_split : (s.cluster_split == 1 ? pick_cluster_split(s, dev, tile) : 1);
@@ -267,6 +307,7 @@ int launch_gemm(const LaunchSpec& s, cudaStream_t stream, int force_tile = 0) {
     tile = 128;
     split = 4;
   }
+  g_last_tile.store(tile | (split << 16), std::memory_order_relaxed);
   if (split > 1) {
     if (tile == 64) return split == 4 ? launch_instance<64, false, false, false, 4>(s, dev, stream)
                                       : launch_instance<64, false, false, false, 2>(s, dev, stream);
@@ -698,6 +739,33 @@ int b200_nvfp4_set_tile_n(int tile_n) {
     return B200_NVFP4_INVALID_ARGUMENT;
   b200::g_tile_n_override.store(tile_n, std::memory_order_relaxed);
   return B200_NVFP4_SUCCESS;
+}
+
+int b200_nvfp4_tune_set(int groups, int rows, int n, int k, int out_f32, int grouped, int tile_n) {
+  if (groups <= 0 || rows <= 0 || n <= 0 || k <= 0 ||
+      (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 256 && tile_n != 512))
+    return B200_NVFP4_INVALID_ARGUMENT;
+  const b200::TuneKey key = b200::tune_key(groups, rows, n, k, out_f32 != 0, grouped != 0);
+  std::lock_guard<std::mutex> lock(b200::g_tune_mutex);
+  if (tile_n == 0) b200::g_tune_table.erase(key);
+  else b200::g_tune_table[key] = tile_n;
+  b200::g_tune_entries.store(static_cast<int>(b200::g_tune_table.size()), std::memory_order_release);
+  return B200_NVFP4_SUCCESS;
+}
+
+int b200_nvfp4_tune_get(int groups, int rows, int n, int k, int out_f32, int grouped) {
+  const b200::TuneKey key = b200::tune_key(groups, rows, n, k, out_f32 != 0, grouped != 0);
+  std::lock_guard<std::mutex> lock(b200::g_tune_mutex);
+  auto it = b200::g_tune_table.find(key);
+  return it == b200::g_tune_table.end() ? 0 : it->second;
+}
+
+int b200_nvfp4_last_launch_tile(void) { return b200::g_last_tile.load(std::memory_order_relaxed); }
+
+void b200_nvfp4_tune_clear(void) {
+  std::lock_guard<std::mutex> lock(b200::g_tune_mutex);
+  b200::g_tune_table.clear();
+  b200::g_tune_entries.store(0, std::memory_order_release);
 }
 
 int b200_nvfp4_set_wait_limit(long long limit_cycles, int withhold_one_arrival) {

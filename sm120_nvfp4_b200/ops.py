@@ -609,3 +609,115 @@ def pack_weights(weight: torch.Tensor, weight_scale: Optional[torch.Tensor] = No
         packed, scales = quantize_expert(w.view(e * n, k), seqlens, cu, scale_m_pad=m_pad)
     packed = packed.view(e, n, k // 2)
     return (packed, scales, alpha) if global_scale else (packed, scales)
+
+
+# ---------------------------------------------------------------------------------- tile table
+#
+# Not in the reference package (its RTX 5090 tuning is compiled in): times the tile shapes of the
+# GEMM kernel on the device for one problem and records the fastest in the library's shape-keyed
+# table (b200_nvfp4_tune_set), which the built-in rules then defer to for exactly that problem.
+
+_TILES = (64, 128, 256, 512)      # 128-row tiles of 64 / 128 / 256 columns on one CTA; 512 = 256 x 256 on a CTA pair
+
+
+def _time_tiles(call, device, candidates, iters: int):
+    """Microseconds per call (CUDA events around `iters` back-to-back calls, three warm-up calls
+    first) for every candidate tile, forced through b200_nvfp4_set_tile_n."""
+    L = _lib.lib()
+    times = {}
+    try:
+        for tile in candidates:
+            _check(tile in _TILES, f"tile must be one of {_TILES}")
+            _lib.check(L.b200_nvfp4_set_tile_n(tile), "set_tile_n")
+            for _ in range(3):
+                call()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(torch.cuda.current_stream(device))
+            for _ in range(iters):
+                call()
+            end.record(torch.cuda.current_stream(device))
+            end.synchronize()
+            times[tile] = start.elapsed_time(end) * 1e3 / iters
+    finally:
+        L.b200_nvfp4_set_tile_n(0)
+    _check(_lib.device_error() == 0, "a kernel reported a timed-out wait while tuning")
+    return times
+
+
+def autotune_gemm(m: int, n: int, k: int, *, batch: int = 1, out_dtype: torch.dtype = torch.float16, device=None,
+                  candidates=_TILES, iters: int = 30, install: bool = True) -> dict:
+    """Times the dense (batch = 1) or batched NVFP4 GEMM of this shape with every candidate tile on
+    random operands and, with install=True, records the fastest for the shape. Returns
+    {"best": tile, "us": {tile: microseconds per call}}. Timing only: the result of a GEMM does not
+    depend on the tile (tests/test_gpu_determinism.py)."""
+    _check(out_dtype in (torch.float16, torch.float32), "out_dtype must be float16 or float32")
+    _check(m > 0 and n > 0 and k > 0 and k % 32 == 0 and n % 8 == 0 and batch > 0,
+           "M, N, K, batch must be positive, K % 32 == 0 and N % 8 == 0")
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    L = _lib.lib()
+    f32 = int(out_dtype == torch.float32)
+    with torch.cuda.device(device):
+        g = torch.Generator(device=device).manual_seed(k * 31 + n)
+        a = torch.randint(0, 256, (batch, m, k // 2), dtype=torch.uint8, device=device, generator=g)
+        b = torch.randint(0, 256, (batch, n, k // 2), dtype=torch.uint8, device=device, generator=g)
+        sfa = torch.randint(0x30, 0x3a, (batch * scale_a_elements(m, n, k),), dtype=torch.uint8, device=device, generator=g)
+        sfb = torch.randint(0x30, 0x3a, (batch * scale_b_elements(m, n, k),), dtype=torch.uint8, device=device, generator=g)
+        out = torch.empty((batch, m, n), dtype=out_dtype, device=device)
+        stream = _stream(device)
+
+        def call():
+            _lib.check(L.b200_nvfp4_gemm(batch, m, n, k, a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
+                                         out.data_ptr(), f32, stream), "gemm")
+
+        times = _time_tiles(call, device, candidates, iters)
+    best = min(times, key=times.get)
+    if install:
+        _lib.check(L.b200_nvfp4_tune_set(batch, m, n, k, f32, 0, best), "tune_set")
+    return {"best": best, "us": times}
+
+
+def autotune_grouped_gemm(seqlens, n: int, k: int, *, device=None, candidates=_TILES, iters: int = 30,
+                          install: bool = True) -> dict:
+    """The same for the grouped GEMM over groups of `seqlens` rows (a representative split: the table
+    is keyed by the number of groups and the total number of rows, the row counts themselves live
+    on the device)."""
+    counts = [int(c) for c in seqlens]
+    _check(len(counts) > 0 and all(c >= 0 for c in counts) and sum(counts) > 0, "seqlens must hold row counts")
+    _check(n > 0 and k > 0 and k % 32 == 0 and n % 8 == 0, "N, K must be positive, K % 32 == 0 and N % 8 == 0")
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    L = _lib.lib()
+    groups, rows = len(counts), sum(counts)
+    m_pad = max(128, (max(counts) + 127) // 128 * 128)
+    with torch.cuda.device(device):
+        g = torch.Generator(device=device).manual_seed(k * 31 + n + groups)
+        x = torch.randint(0, 256, (rows, k // 2), dtype=torch.uint8, device=device, generator=g)
+        w = torch.randint(0, 256, (groups, n, k // 2), dtype=torch.uint8, device=device, generator=g)
+        xs = torch.randint(0x30, 0x3a, (groups * m_pad * scale_k_padded(k),), dtype=torch.uint8, device=device, generator=g)
+        ws = torch.randint(0x30, 0x3a, (groups * scale_b_elements(1, n, k),), dtype=torch.uint8, device=device, generator=g)
+        seq = torch.tensor(counts, dtype=torch.int32, device=device)
+        cu = torch.zeros(groups + 1, dtype=torch.int32, device=device)
+        cu[1:] = torch.cumsum(seq, 0)
+        out = torch.empty((rows, n), dtype=torch.float16, device=device)
+        stream = _stream(device)
+        avg = max(1, rows // groups)
+
+        def call():
+            _lib.check(L.b200_nvfp4_grouped_gemm(out.data_ptr(), x.data_ptr(), w.data_ptr(), seq.data_ptr(),
+                                                 cu.data_ptr(), xs.data_ptr(), ws.data_ptr(), None, None, None, groups,
+                                                 rows, n, k, m_pad, avg, 1, None, stream), "grouped_gemm")
+
+        times = _time_tiles(call, device, candidates, iters)
+    best = min(times, key=times.get)
+    if install:
+        _lib.check(L.b200_nvfp4_tune_set(groups, rows, n, k, 0, 1, best), "tune_set")
+    return {"best": best, "us": times}
+
+
+def tuned_tile(rows: int, n: int, k: int, *, groups: int = 1, out_dtype: torch.dtype = torch.float16,
+               grouped: bool = False) -> int:
+    """The table's tile for a problem (0 = none: the built-in rules apply)."""
+    return int(_lib.lib().b200_nvfp4_tune_get(groups, rows, n, k, int(out_dtype == torch.float32), int(grouped)))
+
+
+def clear_tuned_tiles() -> None:
+    _lib.lib().b200_nvfp4_tune_clear()

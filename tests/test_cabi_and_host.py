@@ -95,3 +95,29 @@ def test_synthetic_data_generators_are_seeded():
     assert all(len(set(r)) == 4 for r in ids.tolist())
     counts, cu = dirichlet_counts(2048, 8, 3)
     assert counts.sum() == 2048 and cu[-1] == 2048
+
+
+def test_tile_table_is_keyed_by_the_whole_problem():
+    # b200_nvfp4_tune_set / _get / _clear: host-side state only, no device needed.
+    import sm120_nvfp4_b200 as pkg
+    from sm120_nvfp4_b200 import _lib
+    L = _lib.lib()
+    pkg.clear_tuned_tiles()
+    assert pkg.tuned_tile(16, 4096, 8192) == 0
+    assert L.b200_nvfp4_tune_set(1, 16, 4096, 8192, 0, 0, 128) == 0
+    assert pkg.tuned_tile(16, 4096, 8192) == 128
+    # every field of the key matters: rows, N, K, groups, output type, dense against grouped
+    assert pkg.tuned_tile(32, 4096, 8192) == 0 and pkg.tuned_tile(16, 4096, 4096) == 0
+    assert pkg.tuned_tile(16, 2048, 8192) == 0 and pkg.tuned_tile(16, 4096, 8192, groups=2) == 0
+    import torch
+    assert pkg.tuned_tile(16, 4096, 8192, out_dtype=torch.float32) == 0
+    assert pkg.tuned_tile(16, 4096, 8192, grouped=True) == 0
+    assert L.b200_nvfp4_tune_set(1, 16, 4096, 8192, 0, 0, 512) == 0      # overwrite
+    assert pkg.tuned_tile(16, 4096, 8192) == 512
+    assert L.b200_nvfp4_tune_set(1, 16, 4096, 8192, 0, 0, 0) == 0        # 0 removes
+    assert pkg.tuned_tile(16, 4096, 8192) == 0
+    for bad in ((0, 16, 64, 64, 0, 0, 64), (1, 0, 64, 64, 0, 0, 64), (1, 16, 64, 64, 0, 0, 96), (1, 16, 64, 64, 0, 0, 1024)):
+        assert L.b200_nvfp4_tune_set(*bad) == _lib.STATUS_INVALID_ARGUMENT
+    L.b200_nvfp4_tune_set(8, 2048, 4096, 8192, 0, 1, 256)
+    pkg.clear_tuned_tiles()
+    assert pkg.tuned_tile(2048, 4096, 8192, groups=8, grouped=True) == 0

@@ -294,3 +294,61 @@ def test_a_wait_that_runs_out_is_reported_and_leaves_the_library_usable(ops, til
     ref32, _ = oracle.gemm(a, b, sfa, sfb)
     check_gemm_parity(got, ref32)
     _no_device_error()
+
+
+def test_tile_rules_table_and_tuner(ops):
+    # What the built-in rules launch for the configurations the reference quotes (tile in the low 16
+    # bits of b200_nvfp4_last_launch_tile, K ranges reduced inside a cluster above), that a table
+    # entry replaces that choice for exactly its problem without changing a bit of the result, and
+    # that the tuner times every candidate and installs the fastest.
+    from sm120_nvfp4_b200 import _lib
+    L = _lib.lib()
+    L.b200_nvfp4_set_tile_n(0)                          # an earlier test may have left its override
+    ops.clear_tuned_tiles()
+
+    def launched():
+        v = L.b200_nvfp4_last_launch_tile()
+        return v & 0xffff, v >> 16
+
+    def operands(m, n, k, seed):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        a = torch.randint(0, 256, (m, k // 2), dtype=torch.uint8, device="cuda", generator=g)
+        b = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda", generator=g)
+        sfa = torch.randint(0x30, 0x3a, (ops.scale_a_elements(m, n, k),), dtype=torch.uint8, device="cuda", generator=g)
+        sfb = torch.randint(0x30, 0x3a, (ops.scale_b_elements(m, n, k),), dtype=torch.uint8, device="cuda", generator=g)
+        return a, b, sfa, sfb
+
+    def run(m, n, k):
+        return ops.cute_gemm(*operands(m, n, k, 71))
+
+    base = run(16, 4096, 8192)
+    assert launched() == (128, 4)                       # skinny: 128-column tiles, K over a cluster of 4
+    run(1024, 4096, 8192)
+    assert launched() == (512, 1)                       # a wave of pair tiles
+    run(16, 4096, 1024)
+    assert launched() == (64, 1)                        # too few k-stages to split: narrow tiles on 64 SMs
+    # the dispatcher's M = 128 path keeps its split whatever the table says
+    assert L.b200_nvfp4_tune_set(1, 128, 4096, 8192, 0, 0, 256) == 0
+    ops.gemm(*operands(128, 4096, 8192, 73))
+    assert launched() == (128, 4)
+    # an entry for the M = 16 problem: the generic entry point follows it, other shapes do not
+    assert L.b200_nvfp4_tune_set(1, 16, 4096, 8192, 0, 0, 256) == 0
+    tuned = run(16, 4096, 8192)
+    assert launched() == (256, 1)
+    assert torch.equal(tuned, base)                     # the tile is not part of the arithmetic
+    run(32, 4096, 8192)
+    assert launched() == (128, 4) and ops.tuned_tile(32, 4096, 8192) == 0
+    ops.clear_tuned_tiles()
+    run(16, 4096, 8192)
+    assert launched() == (128, 4)
+    # the tuner: every candidate timed, the fastest installed and used
+    res = ops.autotune_gemm(64, 1024, 512, iters=5)
+    assert sorted(res["us"]) == [64, 128, 256, 512] and all(t > 0 for t in res["us"].values())
+    assert res["best"] == min(res["us"], key=res["us"].get) == ops.tuned_tile(64, 1024, 512)
+    run(64, 1024, 512)
+    assert launched()[0] == res["best"]
+    res_g = ops.autotune_grouped_gemm([100, 0, 300, 50], 512, 256, iters=5, candidates=(128, 512))
+    assert sorted(res_g["us"]) == [128, 512]
+    assert ops.tuned_tile(450, 512, 256, groups=4, grouped=True) == res_g["best"]
+    ops.clear_tuned_tiles()
+    _no_device_error()
