@@ -162,6 +162,12 @@ def test_peer_memory_hand_off_emulated_on_one_gpu(backend, world, handoff, retur
             got = out.cpu().numpy().astype(np.float32)
             frob = np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)
             assert frob < 2e-2, (call, r, frob)
+            # the BF16 form of the final sum: the same FP32 sums, rounded to 8 significant bits
+            out_b = layers[r].p2p_finish(ret_pos[r], out_bf16=True)
+            torch.cuda.synchronize()
+            assert out_b.dtype == torch.bfloat16
+            diff = (out_b.float() - out.float()).abs()
+            assert bool((diff <= out.float().abs() * 2.0 ** -8 + 2.0 ** -20).all())
     assert _lib.device_error() == 0                          # no wait ran out
 
 
