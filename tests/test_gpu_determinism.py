@@ -94,3 +94,56 @@ def test_many_ragged_groups_finish_without_a_timed_out_wait(ops, tile_n):
     junk = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     _repeat(lambda: ops.grouped_gemm(x, w, dc, dcu, xs, ws), 60, junk)
     assert _lib.device_error() == 0
+
+
+def test_calls_replayed_from_a_cuda_graph_give_the_eager_bits(ops):
+    # The library enqueues on the caller's stream and neither allocates nor synchronises, so a sequence
+    # of calls can be captured into a CUDA graph and replayed: a skinny GEMM (cluster split-K), the
+    # dispatcher's M = 128 path, the token quantiser and a whole fused-MoE layer (routing, both grouped
+    # GEMMs, the reduce), captured once after an eager warm-up, replayed - also on new inputs in the
+    # same buffers - against the eager results bit for bit.
+    from helpers import topk_routing
+    g = torch.Generator(device="cuda").manual_seed(9)
+
+    def rnd(shape, lo=0, hi=256):
+        return torch.randint(lo, hi, shape, dtype=torch.uint8, device="cuda", generator=g)
+
+    n, k = 1024, 2048
+    a16, a128, b = rnd((16, k // 2)), rnd((128, k // 2)), rnd((n, k // 2))
+    sfa16, sfa128 = rnd((ops.scale_a_elements(16, n, k),), 0x30, 0x3a), rnd((ops.scale_a_elements(128, n, k),), 0x30, 0x3a)
+    sfb = rnd((ops.scale_b_elements(1, n, k),), 0x30, 0x3a)
+    experts, hidden, inter, topk, tokens = 8, 256, 128, 2, 48
+    gw, dw = rnd((experts, 2 * inter, hidden // 2)), rnd((experts, hidden, inter // 2))
+    gws = rnd((experts, ops.scale_b_elements(1, 2 * inter, hidden)), 0x28, 0x30)
+    dws = rnd((experts, ops.scale_b_elements(1, hidden, inter)), 0x28, 0x30)
+    x = torch.randn((tokens, hidden), device="cuda", generator=g).to(torch.bfloat16)
+    ids_np, w_np = topk_routing(tokens, experts, topk, 5)
+    ids, wts = torch.from_numpy(ids_np).cuda(), torch.from_numpy(w_np).cuda()
+    seq = torch.tensor([tokens], dtype=torch.int32, device="cuda")
+    cu = torch.tensor([0, tokens], dtype=torch.int32, device="cuda")
+
+    def work():
+        xq, xs = ops.quantize_expert(x, seq, cu, scale_m_pad=128)
+        return (ops.cute_gemm(a16, b, sfa16, sfb), ops.gemm(a128, b, sfa128, sfb),
+                ops.fused_moe(xq, xs.flatten(), gw, gws, dw, dws, ids, wts))
+
+    eager = [t.clone() for t in work()]                 # also the warm-up: one-time set-up happens here
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = work()
+    for _ in range(3):
+        for t in captured:
+            t.fill_(0)
+        graph.replay()
+        torch.cuda.synchronize()
+        for got, want in zip(captured, eager):
+            assert torch.equal(got, want)
+    # new inputs in the same buffers: the replay computes on what is there now
+    a16.copy_(rnd((16, k // 2)))
+    x.copy_(torch.randn((tokens, hidden), device="cuda", generator=g).to(torch.bfloat16))
+    graph.replay()
+    torch.cuda.synchronize()
+    replayed = [t.clone() for t in captured]
+    for got, want in zip(replayed, work()):
+        assert torch.equal(got, want)
