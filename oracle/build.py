@@ -22,7 +22,8 @@ import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-REFERENCE = Path(os.environ.get("NVFP4_REFERENCE_DIR", "/root/reference"))
+# the reference checkout: NVFP4_REFERENCE_DIR, else a directory named "reference" beside this repository
+REFERENCE = Path(os.environ.get("NVFP4_REFERENCE_DIR", HERE.parent.parent / "reference"))
 
 
 def _newer(target: Path, *sources: Path) -> bool:

@@ -27,6 +27,7 @@ What comes from the reference itself:
 from __future__ import annotations
 
 import ast
+import os
 import sys
 from pathlib import Path
 
@@ -35,7 +36,8 @@ import torch
 
 ROOT = Path(__file__).resolve().parents[2]
 sys.path.insert(0, str(ROOT))
-REFERENCE = Path("/root/reference")
+# the reference checkout: NVFP4_REFERENCE_DIR, else a directory named "reference" beside this repository
+REFERENCE = Path(os.environ.get("NVFP4_REFERENCE_DIR", ROOT.parent / "reference"))
 OUT = Path(__file__).resolve().parent
 
 
