@@ -114,10 +114,10 @@ def expected_ep_output(xb, ids, w, gw, gws, dw, dws, world):
     return oracle.reduce(stacked, pos, np.ones((tokens, world), np.float32))
 
 
-def _case(world):
+def _case(world, hidden=128):
     import oracle
     from helpers import randn_quantized, topk_routing
-    experts, hidden, inter, topk, tokens = 8, 128, 64, 3, 37
+    experts, inter, topk, tokens = 8, 64, 3, 37
     rng = np.random.default_rng(3)
     L = oracle.lib()
     gw = np.empty((experts, 2 * inter, hidden // 2), np.uint8)

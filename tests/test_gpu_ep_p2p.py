@@ -28,7 +28,8 @@ def _worker(rank, world, port, result_dir):
     try:
         from sm120_nvfp4_b200.ep import ExpertParallelMoE
         from test_ep_gloo import _case, expected_ep_output
-        experts, hidden, inter, gw, gws, dw, dws, per_rank = _case(world)
+        # hidden = 256: two column blocks of 128 for the pipelined return path
+        experts, hidden, inter, gw, gws, dw, dws, per_rank = _case(world, hidden=256)
         e_local = experts // world
         sl = slice(rank * e_local, (rank + 1) * e_local)
         weights = [torch.from_numpy(a[sl].copy()).to(dev) for a in (gw, gws, dw, dws)]
