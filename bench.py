@@ -715,6 +715,88 @@ def moe_reading(weights: MoeWeights, tokens_per_rank: int, label: str, steps: in
     return reading
 
 
+def moe_stage_times(weights: MoeWeights, tokens: int, iters: int, peaks):
+    """The one-GPU layer stage by stage through the C ABI (the calls b200_nvfp4_fused_moe makes), a CUDA
+    event after every stage - what the reference's benchmarks/benchmark_moe_ops.py:79-109 times per
+    operator. Per stage: mean microseconds, algorithmic bytes, GB/s against the measured copy bandwidth,
+    and for the two grouped GEMMs TFLOP/s. An L2 flush precedes every pass, not every stage: the stages
+    see the cache state the layer leaves them."""
+    import sm120_nvfp4_b200 as ops
+    from sm120_nvfp4_b200 import _lib
+    from sm120_nvfp4_b200.ops import scale_k_padded
+    L = _lib.lib()
+    w, dev = weights, weights.device
+    t, h, inter, k, e = tokens, weights.h, weights.i, weights.k, weights.e_local
+    a = t * k
+    in_pad = m_pad = align(t, 128)
+    g = torch.Generator(device=dev).manual_seed(0xB2000490)
+    x = torch.randn((t, h), device=dev, generator=g).to(torch.bfloat16)
+    logits = torch.randn((t, weights.e), device=dev, generator=g)
+    seq1 = torch.tensor([t], dtype=torch.int32, device=dev)
+    cu1 = torch.tensor([0, t], dtype=torch.int32, device=dev)
+    u8, i32 = dict(dtype=torch.uint8, device=dev), dict(dtype=torch.int32, device=dev)
+    gin, gin_s = torch.empty((a, h // 2), **u8), torch.empty((e, m_pad * scale_k_padded(h)), **u8)
+    din, din_s = torch.empty((a, inter // 2), **u8), torch.empty((e, m_pad * scale_k_padded(inter)), **u8)
+    dout = torch.empty((a, h), dtype=torch.float16, device=dev)
+    pos, seq, cu = torch.empty((t, k), **i32), torch.empty(e, **i32), torch.empty(e + 1, **i32)
+    out = torch.empty((t, h), dtype=torch.bfloat16, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    avg = max(1, a // e)
+    state = {}
+
+    def stages():
+        yield "router_topk", lambda: state.update(zip(("ids", "wts"), ops.router_topk(logits, k)))
+        yield "quantize_tokens", lambda: state.update(zip(("xq", "xs"), ops.quantize_expert(x, seq1, cu1, scale_m_pad=in_pad)))
+        yield "count_and_gather", lambda: _lib.check(L.b200_nvfp4_moe_count_and_gather(
+            gin.data_ptr(), gin_s.data_ptr(), state["xq"].data_ptr(), state["xs"].data_ptr(), state["ids"].data_ptr(),
+            pos.data_ptr(), seq.data_ptr(), cu.data_ptr(), t, h, k, e, 0, in_pad, m_pad, 0, stream), "count_and_gather")
+        yield "gate_up_gemm_silu_quant", lambda: _lib.check(L.b200_nvfp4_grouped_gemm_swiglu_quant(
+            din.data_ptr(), din_s.data_ptr(), gin.data_ptr(), w.gw.data_ptr(), seq.data_ptr(), cu.data_ptr(),
+            gin_s.data_ptr(), w.gws.data_ptr(), None, None, e, a, inter, h, m_pad, m_pad, avg, stream), "gate/up")
+        yield "down_gemm", lambda: _lib.check(L.b200_nvfp4_grouped_gemm(
+            dout.data_ptr(), din.data_ptr(), w.dw.data_ptr(), seq.data_ptr(), cu.data_ptr(), din_s.data_ptr(),
+            w.dws.data_ptr(), None, None, None, e, a, h, inter, m_pad, avg, 1, None, stream), "down")
+        yield "reduce", lambda: _lib.check(L.b200_nvfp4_moe_reduce(
+            out.data_ptr(), dout.data_ptr(), pos.data_ptr(), state["wts"].data_ptr(), None, t, h, k, 1, stream), "reduce")
+
+    sf = lambda rows, kk: rows * (kk // 16)
+    algorithmic = {
+        "router_topk": 4 * t * weights.e + 8 * t * k,
+        "quantize_tokens": t * (2 * h + h // 2 + h // 16),
+        "count_and_gather": 2 * a * (h // 2 + h // 16) + 8 * a,
+        "gate_up_gemm_silu_quant": e * 2 * inter * h // 2 + sf(e * 2 * inter, h) + a * (h // 2 + h // 16) + a * (inter // 2 + inter // 16),
+        "down_gemm": e * h * inter // 2 + sf(e * h, inter) + a * (inter // 2 + inter // 16) + a * 2 * h,
+        "reduce": t * (k * 2 * h + 2 * h),
+    }
+    flops = {"gate_up_gemm_silu_quant": 2.0 * a * 2 * inter * h, "down_gemm": 2.0 * a * h * inter}
+    names = [n for n, _ in stages()]
+    sums = dict.fromkeys(names, 0.0)
+    for it in range(iters + 2):
+        flush.zero_()
+        evs = [torch.cuda.Event(enable_timing=True)]
+        evs[0].record()
+        for _, call in stages():
+            call()
+            evs.append(torch.cuda.Event(enable_timing=True))
+            evs[-1].record()
+        evs[-1].synchronize()
+        if it >= 2:                                   # two warm-up passes
+            for i, n in enumerate(names):
+                sums[n] += evs[i].elapsed_time(evs[i + 1])
+    result, total = [], 0.0
+    for n in names:
+        us = sums[n] / iters * 1e3
+        total += us
+        entry = {"stage": n, "us": us, "algorithmic_bytes": algorithmic[n], "gbs": algorithmic[n] / (us * 1e-6) / 1e9,
+                 "frac_of_measured_hbm": algorithmic[n] / (us * 1e-6) / 1e9 / peaks["hbm_gbs"]}
+        if n in flops:
+            entry["tflops"] = flops[n] / (us * 1e-6) / 1e12
+        result.append(entry)
+    return {"stages": result, "sum_us": total, "iters": iters,
+            "note": "C-ABI calls of the fused layer issued one by one with a CUDA event after each; one L2 flush per pass"}
+
+
 def moe_block(world, rank, device, peaks, steps: int, warmup: int, experts: int = 256):
     weights = MoeWeights(world, rank, device, experts=experts)
     block = {"config": {"workload": "fused_moe_deepseek_v3_shape", "hidden": weights.h, "intermediate": weights.i,
@@ -723,6 +805,7 @@ def moe_block(world, rank, device, peaks, steps: int, warmup: int, experts: int 
     if world == 1:
         block["single"] = moe_reading(weights, 4096, "T=4096 on one GPU", steps, warmup, peaks)
         block["tokens_per_s"] = block["single"]["tokens_per_s"]
+        block["stage_times"] = moe_stage_times(weights, 4096, min(steps, 20), peaks)
     else:
         block["weak"] = moe_reading(weights, 4096, f"weak scaling: T=4096 per rank, {4096 * world} in total",
                                     steps, warmup, peaks)
