@@ -239,16 +239,14 @@ class ExpertParallelMoE:
         self.wait_limit = int(barrier_limit_cycles)
         # p2p transport: the down projection in this many column blocks; the partial rows of a
         # finished block go back to their sources on a second stream while the next one is computed
-        # (0 = choose: two blocks on up to 4 ranks whose slots hold 16384 rows or more - measured on
-        # 4 GPUs, T = 4096 per rank: 1.45 -> 1.33 ms per layer; with 1024 tokens per rank one block is
-        # faster, on 2 GPUs the return stores are too short to matter, and on 8 GPUs they take
-        # several times the down projection, so there is nothing to hide them behind: 1.59 against
-        # 1.62 ms)
+        # (0 = choose: two blocks where the slots of a rank hold 16384 rows or more - measured with
+        # T = 4096 per rank, P50 per layer: 4 GPUs 1.45 -> 1.35 ms, 8 GPUs 1.69 -> 1.53 ms; with 4096
+        # tokens in total one block is faster (4 GPUs 0.577 against 0.588 ms, 8 GPUs 0.406 against
+        # 0.412), and on 2 GPUs the return stores are too short to matter)
         self.return_blocks = int(return_blocks)
         hidden_size = gate_up_weight.shape[2] * 2
         if self.return_blocks == 0:
-            big = (transport == "p2p" and emulate is None and self.world <= 4 and
-                   self.world * int(max_tokens) >= 16384)
+            big = transport == "p2p" and emulate is None and self.world * int(max_tokens) >= 16384
             self.return_blocks = 2 if big and hidden_size % 256 == 0 else 1
         if self.return_blocks < 1 or hidden_size % (128 * self.return_blocks) != 0:
             raise ValueError("return_blocks must divide the hidden size into multiples of 128 columns")
