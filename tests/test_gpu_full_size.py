@@ -132,8 +132,10 @@ def test_config4_full_size_moe_sampled_tokens_and_properties(ops):
     got = out[sel_t].cpu().numpy()
     num = np.linalg.norm(got.astype(np.float64) - want.astype(np.float64))
     den = np.linalg.norm(want.astype(np.float64))
-    assert num / den < 2e-2, num / den                              # same gate as the small-layer test
+    # (the small-layer test's gate is 2e-2; on this data the layer has so far matched the oracle bit for
+    # bit - measured 0.0 - so the full-size gate is held twenty times tighter)
+    assert num / den < 1e-3, num / den
     # and token by token: no sampled token is off by more than the gate either
     per_token = (np.linalg.norm(got.astype(np.float64) - want.astype(np.float64), axis=1) /
                  np.maximum(np.linalg.norm(want.astype(np.float64), axis=1), 1e-30))
-    assert per_token.max() < 2e-2, (int(per_token.argmax()), float(per_token.max()))
+    assert per_token.max() < 1e-3, (int(per_token.argmax()), float(per_token.max()))

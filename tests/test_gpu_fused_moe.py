@@ -323,12 +323,13 @@ def test_full_moe_random_vs_oracle(ops, tokens, experts, topk, hidden, inter, ra
     out = ops.fused_moe(gx, gxs.flatten(), _dev(gw), _dev(gs), _dev(dw), _dev(ds), _dev(ids), _dev(w),
                         shared_output=_dev(shared), ep_rank=rank_ep, num_experts=experts)
     got = out.cpu().numpy()
-    # end to end the two sides re-quantise FP16 intermediates that may differ in the last bit,
-    # so the layer output is held to a relative-Frobenius gate of 2e-2 (the reference's own
-    # analytic check uses rtol .02 / RMSE .003, docs/OPERATOR_MILESTONE.md:103-116)
+    # end to end the two sides re-quantise FP16 intermediates that could differ in the last bit (the
+    # reference's own analytic check allows rtol .02 / RMSE .003, docs/OPERATOR_MILESTONE.md:103-116).
+    # Measured on B200 the three layers match the oracle bit for bit (relative Frobenius error 0.0),
+    # so the gate is held at 1e-3, twenty times tighter than the reference's.
     num = np.linalg.norm(got.astype(np.float64) - want.astype(np.float64))
     den = np.linalg.norm(want.astype(np.float64))
-    assert np.isfinite(got).all() and num / den < 2e-2, num / den
+    assert np.isfinite(got).all() and num / den < 1e-3, num / den
 
 
 @pytest.mark.parametrize("tokens,experts,topk", [(4096, 256, 8), (77, 8, 3), (5, 40, 40), (300, 1000, 6), (9, 4096, 8)])
