@@ -161,7 +161,7 @@ def test_peer_memory_hand_off_emulated_on_one_gpu(backend, world, handoff, retur
             want = expected_ep_output(xb, ids, w, gw, gws, dw, dws, world).astype(np.float32)
             got = out.cpu().numpy().astype(np.float32)
             frob = np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)
-            assert frob < 2e-2, (call, r, frob)
+            assert frob < 1e-3, (call, r, frob)
             # the BF16 form of the final sum: the same FP32 sums, rounded to 8 significant bits
             out_b = layers[r].p2p_finish(ret_pos[r], out_bf16=True)
             torch.cuda.synchronize()
