@@ -22,7 +22,13 @@ def fp16_ulp(y: np.ndarray) -> np.ndarray:
 
 def check_gemm_parity(got: np.ndarray, ref32: np.ndarray, rowmax: np.ndarray | None = None):
     """The GEMM gate: relative Frobenius error <= 1e-3 and, per element,
-    |diff| <= 2 FP16 ulp(ref) + 1e-3 * max|ref| of the row."""
+    |diff| <= 2 FP16 ulp(ref) + 1e-3 * max|ref| of the row. For FP16 outputs also: at least 99 % of
+    the elements are exactly the oracle's FP32 value rounded to FP16 (measured on B200: 100 % at every
+    full-size configuration, K = 8192 included - the accumulation order inside the tensor core does
+    not show at FP16 precision)."""
+    if got.dtype == np.float16 and got.size:
+        exact = float((got == ref32.astype(np.float32).astype(np.float16)).mean())
+        assert exact >= 0.99, f"only {exact:.4f} of the FP16 outputs equal the rounded oracle value"
     got = got.astype(np.float32)
     ref32 = ref32.astype(np.float32)
     assert np.isfinite(got).all(), "non-finite output"
