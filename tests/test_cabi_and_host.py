@@ -121,3 +121,30 @@ def test_tile_table_is_keyed_by_the_whole_problem():
     L.b200_nvfp4_tune_set(8, 2048, 4096, 8192, 0, 1, 256)
     pkg.clear_tuned_tiles()
     assert pkg.tuned_tile(2048, 4096, 8192, groups=8, grouped=True) == 0
+
+
+def test_hand_off_and_window_entry_points_validate_without_gpu():
+    # The entry points added for the expert-parallel hand-off and the column-window GEMM reject bad
+    # arguments before any CUDA call (dummy non-null pointers, 16-byte aligned).
+    import ctypes
+    from sm120_nvfp4_b200 import _lib
+    L = _lib.lib()
+    bad = _lib.STATUS_INVALID_ARGUMENT
+    p = 4096
+    # column window: start not a multiple of 128, inner window not a multiple of 128, past the end, empty
+    for start, count in ((64, 128), (0, 200), (640, 128), (0, 0), (-128, 128)):
+        assert L.b200_nvfp4_grouped_gemm_columns(p, p, p, p, p, p, p, 3, 440, 648, 256, 384, 150, None, start, count,
+                                                 None) == bad
+    table = (ctypes.c_void_p * 2)(p, p)
+    assert L.b200_nvfp4_ep_publish_p2p(table, 2, 2, 0, 1, None) == bad          # rank outside the world
+    assert L.b200_nvfp4_ep_publish_p2p(table, 0, 65, 0, 1, None) == bad         # more ranks than the flag area holds
+    assert L.b200_nvfp4_ep_publish_p2p(table, 0, 2, -1, 1, None) == bad
+    assert L.b200_nvfp4_ep_publish_p2p((ctypes.c_void_p * 2)(p, None), 0, 2, 0, 1, None) == bad
+    assert L.b200_nvfp4_ep_sum_p2p(p, p, p, 4, 130, 2, 0, p, 1, 0, None) == bad  # hidden not a multiple of 8
+    assert L.b200_nvfp4_ep_sum_p2p(p, p, p, 0, 128, 2, 0, p, 1, 0, None) == bad
+    assert L.b200_nvfp4_ep_sum_p2p(p, p, p, 4, 128, 2, 0, p + 2, 1, 0, None) == bad   # misaligned ready words
+    assert L.b200_nvfp4_ep_sum_p2p(p, p, p, 4, 128, 2, 0, p, 1, -5, None) == bad       # negative limit
+    assert L.b200_nvfp4_ep_unpack_slots_ready(p, p, p, p, p, p, 2, 4, 128, 2, p + 1, 1, 0, None) == bad
+    assert L.b200_nvfp4_ep_unpack_slots_ready(p, p, p, p, p, p, 2, 4, 128, 2, p, 1, -1, None) == bad
+    for start, count in ((4, 64), (0, 0), (0, 132), (128, 64)):
+        assert L.b200_nvfp4_ep_reduce_return_p2p_columns(table, p, p, p, p, 0, 2, 4, 128, 2, start, count, None) == bad
